@@ -29,9 +29,14 @@ def register_architecture(name: str, parse_config, build_spec) -> None:
 
 
 def architecture_name(config_dict: dict) -> str:
+    """The name a config.json declares: `architectures[0]`, or the string under `architecture`."""
+    one = config_dict.get("architecture")
+    if "architectures" not in config_dict and isinstance(one, str) and one:
+        return one
     archs = config_dict.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("missing/invalid config key: architectures (a non-empty list of names)")
+        raise ConfigError("missing/invalid config key: architectures (a non-empty list of names; or "
+                          "architecture, one name)")
     return archs[0]
 
 

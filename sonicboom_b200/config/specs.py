@@ -62,13 +62,27 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class DepthMixSpec:
+    """What goes on to the next schedule entry instead of a block's own result: a combination of
+    the embedding output and every block result so far (`n_inputs` of them, this block's last)."""
+    kind: str                      # key of parts.DEPTH_MIXES, e.g. "weighted_sum"
+    n_inputs: int
+    tensor: str                    # tensor name of the coefficients, [n_inputs]
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One block: which arrangement, and the parts it arranges."""
+    """One block: which arrangement, and the parts it arranges.  An arrangement that norms a
+    sublayer's result before the residual add names those norms in the `*_post_norm` fields; a
+    block without a feed-forward has `feed_forward` (and its norms) None."""
     arrangement: str               # key of parts.BLOCKS, e.g. "pre_norm"
     mixer: MixerSpec
     mixer_norm: NormSpec
-    feed_forward: FeedForwardSpec
-    feed_forward_norm: NormSpec
+    feed_forward: Optional[FeedForwardSpec]
+    feed_forward_norm: Optional[NormSpec]
+    mixer_post_norm: Optional[NormSpec] = None
+    feed_forward_post_norm: Optional[NormSpec] = None
+    depth_mix: Optional[DepthMixSpec] = None
 
     @property
     def kind(self) -> str:
@@ -115,3 +129,7 @@ class ModelSpec:
                 if self.schedule[e.cache_from].cache_from is not None:
                     raise ConfigError(f"schedule[{i}] reads the cache of entry {e.cache_from}, "
                                       "which owns none")
+            mix = self.layers[e.layer].depth_mix
+            if mix is not None and mix.n_inputs != i + 2:
+                raise ConfigError(f"schedule[{i}] mixes {mix.n_inputs} streams, but the embedding output "
+                                  f"and the block results so far are {i + 2}")

@@ -17,7 +17,7 @@ namespace {
 
 constexpr int CHUNK = 256;
 constexpr int THREADS = 128;
-constexpr int MAX_HD = 256;
+constexpr int MAX_HD = 1024;
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(THREADS)

@@ -52,6 +52,13 @@ __device__ __forceinline__ __nv_bfloat16 sb_from_f32<__nv_bfloat16>(float v) {
 // (core/src/nn/activation.cpp:41-50, core/src/nn/cuda_elementwise.cu:203-212).
 __device__ __forceinline__ float sb_silu(float x) { return x / (1.0f + expf(-x)); }
 
+// The gated activation with clamped factors: a = min(gate, limit), b = clamp(up, -limit, limit),
+// y = a * sigmoid(alpha a) * (b + 1), every step in float32 with the accurate expf.
+__device__ __forceinline__ float sb_glu_clamped(float gate, float up, float limit, float alpha) {
+  const float a = fminf(gate, limit), b = fminf(fmaxf(up, -limit), limit);
+  return a / (1.0f + expf(-alpha * a)) * (b + 1.0f);
+}
+
 // The rotation of one pair (a at index i, b at i + rot/2): lo = a cos - b sin, hi = a sin + b cos,
 // every product and the sum rounded on its own (no fused multiply-add), so that every kernel
 // that rotates gives the same bits whatever the compiler would contract.

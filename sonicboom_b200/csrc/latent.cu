@@ -1,0 +1,199 @@
+// Kernels of attention over a cached low-rank latent.
+//
+// The cache holds, per token, the normed latent c (rank values) and one rotated key part kr
+// (rd values) that all heads share.  With per-head matrices Uk [dim, rank] and Uv [vdim, rank]
+// the score of head h is  q_h . (Uk_h c) + qr_h . kr = (Uk_h^T q_h) . c + qr_h . kr  and the
+// head's output is  Uv_h (sum_j p_j c_j):  attention with ONE key/value head whose key row is
+// [c | kr] and whose value row is c, between a product per head before it (q_h -> Uk_h^T q_h) and
+// one after it.  So the paged attention kernels run unchanged on a cache entry with one head of
+// size rank + rd (the value plane carries c and zeros), and this file supplies the rest:
+//
+//   sb_latent_prep:  finishes the fused projection row [q heads | latent | key part]: RMS norm
+//                    of the latent, rotation of every head's rd part and of the key part, the
+//                    cache write, and the rotated query parts into the wide query rows;
+//   sb_head_linear:  out[r, h, :] = W[h] in[r, h, :], a small product per head over strided rows.
+//
+// Rotation: interleaved pairs.  Of a rotated vector, elements 2i and 2i + 1 (i < rot / 2) turn by
+// the angle float(pos) * inv_freq[i]; elements from `rot` on pass unchanged.
+#include "common.cuh"
+
+namespace {
+
+constexpr int PREP_THREADS = 128;
+constexpr int MAX_ROT_PAIRS = 512;
+
+template <typename TW, typename TC, typename TQ>
+__global__ void __launch_bounds__(PREP_THREADS)
+latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int rank, int rot,
+                   const float* __restrict__ inv_freq, const int32_t* row_seq, const int32_t* row_pos,
+                   const int32_t* page_off, const int32_t* page_ids, int page_size,
+                   const TW* __restrict__ cnorm, float eps, TC* cache, TQ* q_wide, int has_kv) {
+  __shared__ float cs[MAX_ROT_PAIRS], sn[MAX_ROT_PAIRS];
+  __shared__ float red[PREP_THREADS / 32 + 1];
+  sb_pdl_launch();
+  const int t = blockIdx.x, tid = threadIdx.x;
+  const int pos = row_pos[t];
+  const int half = rot >> 1;
+  for (int i = tid; i < half; i += PREP_THREADS) {
+    const float theta = (float)pos * inv_freq[i];
+    cs[i] = cosf(theta);
+    sn[i] = sinf(theta);
+  }
+  int page = -1;
+  if (has_kv) {
+    const int seq = row_seq[t];
+    const int first = page_off[seq], n = page_off[seq + 1] - first;
+    const int i = pos / page_size;
+    page = (pos >= 0 && i < n) ? page_ids[first + i] : -1;
+  }
+  __syncthreads();
+  sb_pdl_wait();
+  const float* src = proj + (size_t)t * ld;
+  const int hw = dim + rd, wide = rank + rd;
+  // the rotated part of every query head, into the tail of its wide query row
+  for (int e = tid; e < n_heads * rd; e += PREP_THREADS) {
+    const int h = e / rd, d = e % rd;
+    const float* qr = src + (size_t)h * hw + dim;
+    float v = qr[d];
+    if (d < rot) {
+      const int i = d >> 1;
+      v = (d & 1) ? sb_rot_hi(qr[d - 1], qr[d], cs[i], sn[i]) : sb_rot_lo(qr[d], qr[d + 1], cs[i], sn[i]);
+    }
+    q_wide[((size_t)t * n_heads + h) * wide + rank + d] = sb_from_f32<TQ>(v);
+  }
+  if (!has_kv) return;
+  const float* lat = src + (size_t)n_heads * hw;
+  float s = 0.0f;
+  for (int i = tid; i < rank; i += PREP_THREADS) s = fmaf(lat[i], lat[i], s);
+  s = sb_warp_sum(s);
+  if ((tid & 31) == 0) red[tid >> 5] = s;
+  __syncthreads();
+  if (tid == 0) {
+    float total = 0.0f;
+    for (int i = 0; i < PREP_THREADS / 32; ++i) total += red[i];
+    red[PREP_THREADS / 32] = 1.0f / sqrtf(total / (float)rank + eps);
+  }
+  __syncthreads();
+  if (page < 0) return;               // no page of its own at that position: nothing is written
+  const float inv = red[PREP_THREADS / 32];
+  TC* krow = cache + (((size_t)page * 2) * page_size + pos % page_size) * wide;
+  TC* vrow = cache + (((size_t)page * 2 + 1) * page_size + pos % page_size) * wide;
+  for (int i = tid; i < rank; i += PREP_THREADS) {
+    const TC c = sb_from_f32<TC>((lat[i] * inv) * sb_to_f32<TW>(cnorm[i]));
+    krow[i] = c;
+    vrow[i] = c;
+  }
+  const float* kr = lat + rank;
+  for (int d = tid; d < rd; d += PREP_THREADS) {
+    float v = kr[d];
+    if (d < rot) {
+      const int i = d >> 1;
+      v = (d & 1) ? sb_rot_hi(kr[d - 1], kr[d], cs[i], sn[i]) : sb_rot_lo(kr[d], kr[d + 1], cs[i], sn[i]);
+    }
+    krow[rank + d] = sb_from_f32<TC>(v);
+    vrow[rank + d] = sb_from_f32<TC>(0.0f);
+  }
+}
+
+// out[r, h, n] = sum_k in[r, h, k] * W[h, n, k], k ascending in float32.  32 x 64 outputs a block,
+// 2 x 4 a thread, K in chunks of 16 through shared memory.
+constexpr int HL_BM = 32, HL_BN = 64, HL_BK = 16, HL_THREADS = 256;
+
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(HL_THREADS)
+head_linear_kernel(const TI* in, size_t in_ld, size_t in_hs, const TW* __restrict__ W, int n_rows,
+                   int N, int K, TO* out, size_t out_ld, size_t out_hs) {
+  __shared__ float As[HL_BK][HL_BM + 1];
+  __shared__ float Ws[HL_BK][HL_BN + 1];
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int h = blockIdx.z, r0 = blockIdx.x * HL_BM, n0 = blockIdx.y * HL_BN;
+  const int tid = threadIdx.x, ty = tid / 16, tx = tid % 16;
+  const TI* a = in + (size_t)h * in_hs;
+  const TW* w = W + (size_t)h * N * K;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += HL_BK) {
+    for (int e = tid; e < HL_BM * HL_BK; e += HL_THREADS) {
+      const int r = e / HL_BK, k = e % HL_BK;
+      As[k][r] = (r0 + r < n_rows && k0 + k < K) ? sb_to_f32<TI>(a[(size_t)(r0 + r) * in_ld + k0 + k]) : 0.0f;
+    }
+    for (int e = tid; e < HL_BN * HL_BK; e += HL_THREADS) {
+      const int n = e / HL_BK, k = e % HL_BK;
+      Ws[k][n] = (n0 + n < N && k0 + k < K) ? sb_to_f32<TW>(w[(size_t)(n0 + n) * K + k0 + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < HL_BK; ++k) {
+      const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = Ws[k][tx + 16 * j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = r0 + ty * 2 + i;
+    if (r >= n_rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n < N) out[(size_t)r * out_ld + (size_t)h * out_hs + n] = sb_from_f32<TO>(acc[i][j]);
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int dim, int rd, int rank,
+                              int rot, const float* inv_freq, const int32_t* row_seq,
+                              const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
+                              int page_size, const void* cnorm, int cnorm_dtype, float eps, void* cache,
+                              int cache_dtype, void* q_wide, int q_dtype, int has_kv, cudaStream_t stream) {
+  if (n_rows <= 0 || n_heads <= 0 || dim < 0 || rd < 0 || rank <= 0 || !proj || !q_wide || !row_pos)
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: rows=%d heads=%d dim=%d rd=%d rank=%d", n_rows, n_heads, dim, rd, rank);
+  if (rot < 0 || rot % 2 || rot > rd || rot / 2 > MAX_ROT_PAIRS)
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: %d rotated dimensions of %d (even, at most %d)", rot, rd, 2 * MAX_ROT_PAIRS);
+  if (rot > 0 && !inv_freq) SB_FAIL(SB_ERR_ARG, "sb_latent_prep: no frequency table");
+  if (has_kv && (!cache || !cnorm || !row_seq || !page_off || !page_ids || page_size <= 0))
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: a cache write needs the cache, its norm weight and the page tables");
+  if (!sb_valid_dtype(q_dtype) || (has_kv && (!sb_valid_dtype(cache_dtype) || !sb_valid_dtype(cnorm_dtype))))
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: dtype codes %d %d %d", q_dtype, cache_dtype, cnorm_dtype);
+  const int ld = n_heads * (dim + rd) + (has_kv ? rank + rd : 0);
+  SB_DISPATCH_DTYPE(has_kv ? cnorm_dtype : SB_F32, TW, {
+    SB_DISPATCH_DTYPE(has_kv ? cache_dtype : SB_F32, TC, {
+      SB_DISPATCH_DTYPE(q_dtype, TQ, {
+        sb_launch<SB_K_ELEMENTWISE>(latent_prep_kernel<TW, TC, TQ>, dim3(n_rows), dim3(PREP_THREADS), 0, stream,
+                                    proj, ld, n_heads, dim, rd, rank, rot, inv_freq, row_seq, row_pos, page_off,
+                                    page_ids, page_size, (const TW*)cnorm, eps, (TC*)cache, (TQ*)q_wide, has_kv);
+      });
+    });
+  });
+  SB_CHECK_LAUNCH("sb_latent_prep");
+  return SB_OK;
+}
+
+extern "C" int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, const void* W,
+                              int w_dtype, int n_rows, int n_heads, int N, int K, void* out, int out_dtype,
+                              size_t out_ld, size_t out_hs, cudaStream_t stream) {
+  if (n_rows <= 0 || n_heads <= 0 || N <= 0 || K <= 0 || !in || !W || !out)
+    SB_FAIL(SB_ERR_ARG, "sb_head_linear: rows=%d heads=%d N=%d K=%d", n_rows, n_heads, N, K);
+  if (n_heads > 65535 || (N + HL_BN - 1) / HL_BN > 65535)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_head_linear: %d heads, %d outputs", n_heads, N);
+  if (!sb_valid_dtype(in_dtype) || !sb_valid_dtype(w_dtype) || !sb_valid_dtype(out_dtype))
+    SB_FAIL(SB_ERR_ARG, "sb_head_linear: dtype codes %d %d %d", in_dtype, w_dtype, out_dtype);
+  const dim3 grid((n_rows + HL_BM - 1) / HL_BM, (N + HL_BN - 1) / HL_BN, n_heads);
+  SB_DISPATCH_DTYPE(in_dtype, TI, {
+    SB_DISPATCH_DTYPE(w_dtype, TW, {
+      SB_DISPATCH_DTYPE(out_dtype, TO, {
+        sb_launch<SB_K_OTHER>(head_linear_kernel<TI, TW, TO>, grid, dim3(HL_THREADS), 0, stream, (const TI*)in, in_ld,
+                              in_hs, (const TW*)W, n_rows, N, K, (TO*)out, out_ld, out_hs);
+      });
+    });
+  });
+  SB_CHECK_LAUNCH("sb_head_linear");
+  return SB_OK;
+}

@@ -138,6 +138,53 @@ void sb_gemm_tc5_pairs(int mode);   /* products of more than 128 rows on pairs o
 void sb_gemm_tc5_force_width(int bn);   /* 256, 240, 224, 208 or 192 for every many-rows product; else by the sizes */
 int sb_gemm_tc5_tile_width(int M, int N, int n_sms);   /* tile width of the many-rows form; 0: that form does not run */
 
+/* ---- residual-stream rows ----
+ * out[r] = x[r] + y[r] / sqrt(mean(y[r]^2) + eps) * w (w has `width` values): a sublayer's result,
+ * normed, joins the stream.  With `normed` non-null the RMS norm of the finished row (weight
+ * next_w, next_eps) is written too, in normed_dtype.  out may be x. */
+int sb_norm_add(const float* y, const float* x, int n_rows, int width, const void* w, int w_dtype,
+                float eps, float* out, const void* next_w, int next_w_dtype, float next_eps,
+                void* normed, int normed_dtype, sb_stream_t stream);
+/* out[r] = sum over j < n_inputs of coef[j] * planes[j * plane + r * width ...], j ascending; the
+ * optional norm of the finished row as in sb_norm_add. */
+int sb_depth_mix(const float* planes, size_t plane, int n_inputs, const void* coef, int coef_dtype,
+                 int n_rows, int width, float* out, const void* next_w, int next_w_dtype,
+                 float next_eps, void* normed, int normed_dtype, sb_stream_t stream);
+/* gu[r] = [gate (ff) | up (ff)]; out[r, c] = a sigmoid(alpha a) (b + 1), a = min(gate, limit),
+ * b = clamp(up, -limit, limit). */
+int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, void* out,
+                   int out_dtype, sb_stream_t stream);
+
+/* ---- attention over a cached latent ----
+ * proj[r] = [n_heads x (dim | rd) | rank | rd] (the last two only with has_kv).  Rotates the first
+ * `rot` values of every rd part in interleaved pairs (2i, 2i + 1) by float(pos) * inv_freq[i];
+ * writes each head's rotated part to q_wide[r, h, rank : rank + rd]; with has_kv, RMS-norms the
+ * latent (weight cnorm, eps) and writes the page row of the position: key plane [latent | rotated
+ * key part], value plane [latent | zeros].  The cache entry has one head of size rank + rd. */
+int sb_latent_prep(const float* proj, int n_rows, int n_heads, int dim, int rd, int rank, int rot,
+                   const float* inv_freq, const int32_t* row_seq, const int32_t* row_pos,
+                   const int32_t* page_off, const int32_t* page_ids, int page_size, const void* cnorm,
+                   int cnorm_dtype, float eps, void* cache, int cache_dtype, void* q_wide, int q_dtype,
+                   int has_kv, sb_stream_t stream);
+/* out[r * out_ld + h * out_hs + n] = sum_k in[r * in_ld + h * in_hs + k] * W[(h * N + n) * K + k] */
+int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, const void* W, int w_dtype,
+                   int n_rows, int n_heads, int N, int K, void* out, int out_dtype, size_t out_ld,
+                   size_t out_hs, sb_stream_t stream);
+
+/* ---- matrix-memory recurrence (mLSTM) ----
+ * proj[r] = [q heads*dim | k heads*dim | v heads*vdim | g heads*vdim | x_i heads | x_f heads] float32.
+ * state: float32 [slot, heads, dim + 1, vdim + 1] (column vdim is the normalizer, row dim the running
+ * maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
+ * state after the last row; num [rows, heads, vdim + 1] and m_row [rows, heads] receive the
+ * numerators and maxima.  sb_mlstm_out divides, norms each head (eps), applies norm_w
+ * [heads*vdim] and the gate sigmoid(g): out [rows, heads*vdim]. */
+int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_row0, const int32_t* seq_slot,
+                  int n_heads, int dim, int vdim, const void* i_bias, const void* f_bias, int bias_dtype,
+                  float cap, float q_scale, float* state, float* num, float* m_row, sb_stream_t stream);
+int sb_mlstm_out(const float* num, const float* m_row, const float* proj, int n_rows, int n_heads,
+                 int dim, int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out,
+                 int out_dtype, sb_stream_t stream);
+
 /* Plain attention over the paged cache (float32 arithmetic, any head size up to 256). */
 int sb_attention_plain(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,
                        const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,

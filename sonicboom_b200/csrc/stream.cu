@@ -1,0 +1,176 @@
+// Row kernels of the residual stream for blocks that norm a sublayer's result before they add
+// it, and for models that feed each layer a weighted sum of everything before it.
+//
+//   sb_norm_add:   out[r] = x[r] + y[r] / sqrt(mean(y[r]^2) + eps) * w
+//   sb_depth_mix:  out[r] = sum_j c[j] * planes[j][r]           (j ascending, float32)
+//
+// Both can also deliver the RMS norm of the row they have just finished (the first norm of
+// whatever runs next) in the activation dtype, so that the row is read once.  One block per
+// row; sums are fixed trees (thread-strided partial sums, warp shuffles, the warps in order), so
+// a row's result does not depend on the other rows of the launch.  All arithmetic is float32.
+#include "common.cuh"
+
+namespace {
+
+constexpr int ROW_THREADS = 256;
+
+// Sum over the block, the same value in every thread.  `red` holds ROW_THREADS / 32 + 1 floats.
+__device__ __forceinline__ float block_sum(float s, float* red) {
+  s = sb_warp_sum(s);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();                       // `red` may still be read from an earlier sum
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.0f;
+    for (int i = 0; i < ROW_THREADS / 32; ++i) total += red[i];
+    red[ROW_THREADS / 32] = total;
+  }
+  __syncthreads();
+  return red[ROW_THREADS / 32];
+}
+
+// Writes normed[i] = out[i] * inv * next_w[i] for the thread's own elements of the row it wrote.
+template <typename TN, typename TO>
+__device__ __forceinline__ void write_normed(const float* o, int width, float sq, float next_eps,
+                                             const TN* __restrict__ next_w, TO* nrm, float* red) {
+  const float total = block_sum(sq, red);
+  const float inv = 1.0f / sqrtf(total / (float)width + next_eps);
+  for (int i = threadIdx.x; i < width; i += ROW_THREADS)
+    nrm[i] = sb_from_f32<TO>((o[i] * inv) * sb_to_f32<TN>(next_w[i]));
+}
+
+template <typename TW, typename TN, typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+norm_add_kernel(const float* y, const float* x, int width, const TW* __restrict__ w, float eps,
+                float* out, const TN* __restrict__ next_w, float next_eps, TO* normed) {
+  __shared__ float red[ROW_THREADS / 32 + 1];
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const size_t r = blockIdx.x;
+  const float* yr = y + r * width;
+  const float* xr = x + r * width;
+  float* o = out + r * width;
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
+    const float v = yr[i];
+    s = fmaf(v, v, s);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(s, red) / (float)width + eps);
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
+    const float v = xr[i] + (yr[i] * inv) * sb_to_f32<TW>(w[i]);
+    o[i] = v;
+    sq = fmaf(v, v, sq);
+  }
+  if (normed) write_normed<TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
+}
+
+constexpr int MIX_MAX = 256;       // most planes one depth mix adds up
+
+template <typename TC, typename TN, typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+depth_mix_kernel(const float* planes, size_t plane, int n_inputs, const TC* __restrict__ coef,
+                 int width, float* out, const TN* __restrict__ next_w, float next_eps, TO* normed) {
+  __shared__ float red[ROW_THREADS / 32 + 1];
+  __shared__ float c[MIX_MAX];
+  sb_pdl_launch();
+  for (int j = threadIdx.x; j < n_inputs; j += ROW_THREADS) c[j] = sb_to_f32<TC>(coef[j]);
+  __syncthreads();
+  sb_pdl_wait();
+  const size_t r = blockIdx.x;
+  float* o = out + r * width;
+  float sq = 0.0f;
+  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
+    const float* p = planes + r * width + i;
+    float v = 0.0f;
+    for (int j = 0; j < n_inputs; ++j) v = fmaf(c[j], p[(size_t)j * plane], v);
+    o[i] = v;
+    sq = fmaf(v, v, sq);
+  }
+  if (normed) write_normed<TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
+}
+
+// y = a * sigmoid(alpha a) * (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit);
+// the input row is [gate (ff) | up (ff)] in float32.
+template <typename TO>
+__global__ void glu_clamped_kernel(const float* gu, size_t n, int ff, float limit, float alpha, TO* out) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = e / ff, c = e % ff;
+    out[e] = sb_from_f32<TO>(sb_glu_clamped(gu[r * 2 * ff + c], gu[r * 2 * ff + ff + c], limit, alpha));
+  }
+}
+
+}  // namespace
+
+#define SB_DISPATCH_NEXT(has, code, TN, ...)  \
+  do {                                         \
+    if (!(has) || (code) == SB_F32) {          \
+      using TN = float;                        \
+      __VA_ARGS__                              \
+    } else {                                   \
+      using TN = __nv_bfloat16;                \
+      __VA_ARGS__                              \
+    }                                          \
+  } while (0)
+
+extern "C" int sb_norm_add(const float* y, const float* x, int n_rows, int width, const void* w,
+                           int w_dtype, float eps, float* out, const void* next_w, int next_w_dtype,
+                           float next_eps, void* normed, int normed_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0 || !y || !x || !w || !out)
+    SB_FAIL(SB_ERR_ARG, "sb_norm_add: rows=%d width=%d", n_rows, width);
+  if (!sb_valid_dtype(w_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
+    SB_FAIL(SB_ERR_ARG, "sb_norm_add: dtype codes %d %d %d", w_dtype, next_w_dtype, normed_dtype);
+  if (!(eps >= 0.0f) || (normed && !(next_eps >= 0.0f))) SB_FAIL(SB_ERR_ARG, "sb_norm_add: eps %g %g", eps, next_eps);
+  SB_DISPATCH_DTYPE(w_dtype, TW, {
+    SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
+      SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
+        sb_launch<SB_K_ELEMENTWISE>(norm_add_kernel<TW, TN, TO>, dim3(n_rows), dim3(ROW_THREADS), 0, stream, y, x,
+                                    width, (const TW*)w, eps, out, (const TN*)next_w, next_eps, (TO*)normed);
+      });
+    });
+  });
+  SB_CHECK_LAUNCH("sb_norm_add");
+  return SB_OK;
+}
+
+extern "C" int sb_depth_mix(const float* planes, size_t plane, int n_inputs, const void* coef,
+                            int coef_dtype, int n_rows, int width, float* out, const void* next_w,
+                            int next_w_dtype, float next_eps, void* normed, int normed_dtype,
+                            cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0 || !planes || !coef || !out)
+    SB_FAIL(SB_ERR_ARG, "sb_depth_mix: rows=%d width=%d", n_rows, width);
+  if (n_inputs < 1 || n_inputs > MIX_MAX)
+    SB_FAIL(SB_ERR_UNSUPPORTED, "sb_depth_mix: %d inputs (1 to %d)", n_inputs, MIX_MAX);
+  if (plane < (size_t)n_rows * width) SB_FAIL(SB_ERR_ARG, "sb_depth_mix: planes overlap");
+  if (!sb_valid_dtype(coef_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
+    SB_FAIL(SB_ERR_ARG, "sb_depth_mix: dtype codes %d %d %d", coef_dtype, next_w_dtype, normed_dtype);
+  SB_DISPATCH_DTYPE(coef_dtype, TC, {
+    SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
+      SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
+        sb_launch<SB_K_ELEMENTWISE>(depth_mix_kernel<TC, TN, TO>, dim3(n_rows), dim3(ROW_THREADS), 0, stream, planes,
+                                    plane, n_inputs, (const TC*)coef, width, out, (const TN*)next_w, next_eps,
+                                    (TO*)normed);
+      });
+    });
+  });
+  SB_CHECK_LAUNCH("sb_depth_mix");
+  return SB_OK;
+}
+
+extern "C" int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, void* out,
+                              int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || ff <= 0 || !gu || !out) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: rows=%d ff=%d", n_rows, ff);
+  if (!sb_valid_dtype(out_dtype)) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: dtype code %d", out_dtype);
+  if (!(limit > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: limit %g must be positive", limit);
+  const size_t n = (size_t)n_rows * ff;
+  const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
+  SB_DISPATCH_DTYPE(out_dtype, TO, {
+    sb_launch<SB_K_ELEMENTWISE>(glu_clamped_kernel<TO>, dim3(blocks), dim3(256), 0, stream, gu, n, ff, limit, alpha,
+                                (TO*)out);
+  });
+  SB_CHECK_LAUNCH("sb_glu_clamped");
+  return SB_OK;
+}

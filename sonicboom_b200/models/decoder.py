@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..config.specs import ModelSpec
-from ..parts import BLOCKS, NORMS, StepContext, make
+from ..parts import BLOCKS, DEPTH_MIXES, NORMS, StepContext, make
 from ..weights.loader import TensorRequest
 
 
@@ -28,6 +28,9 @@ class DecoderModel:
         self.blocks = [make(BLOCKS, "block arrangement", l, dtype, device)
                        for l in spec.layers]
         self.final_norm = make(NORMS, "norm", spec.final_norm, dtype, device)
+        # per layer: what is handed on instead of the block's own result (None: the result itself)
+        self.depth_mixes = [make(DEPTH_MIXES, "depth mix", l.depth_mix, dtype, device)
+                            if l.depth_mix is not None else None for l in spec.layers]
         for i, e in enumerate(spec.schedule):
             if e.cache_from is not None:
                 mine = self.blocks[e.layer].kv_need()
@@ -42,8 +45,10 @@ class DecoderModel:
     def tensor_requests(self) -> list[TensorRequest]:
         s = self.spec
         req = [TensorRequest(s.embedding_tensor, (s.vocab, s.width), "embedding")]
-        for b in self.blocks:
+        for b, m in zip(self.blocks, self.depth_mixes):
             req += b.tensor_requests()
+            if m is not None:
+                req += m.tensor_requests()
         req += self.final_norm.tensor_requests()
         if s.head_tensor is not None:
             req.append(TensorRequest(s.head_tensor, (s.vocab, s.width)))
@@ -54,8 +59,10 @@ class DecoderModel:
 
     def bind(self, get) -> None:
         self.embedding = get(self.spec.embedding_tensor)
-        for b in self.blocks:
+        for b, m in zip(self.blocks, self.depth_mixes):
             b.bind(get)
+            if m is not None:
+                m.bind(get)
         self.final_norm.bind(get)
         self.head = self.embedding if self.spec.head_tensor is None else get(self.spec.head_tensor)
 
@@ -73,26 +80,66 @@ class DecoderModel:
         """Runs the step's rows through every schedule entry; returns float32 logits
         [len(plan.want_rows), vocab] (None when no logits are wanted)."""
         s = self.spec
-        x = torch.empty((plan.n_rows, s.width), dtype=torch.float32, device=self.device)
+        n = len(s.schedule)
+        mixes = [self.depth_mixes[e.layer] for e in s.schedule]
+        # With depth mixing the embedding output and every block result of the step are kept side
+        # by side: streams[0] is the embedding output, streams[i + 1] the result of entry i.
+        streams = torch.empty((n + 1, plan.n_rows, s.width), dtype=torch.float32, device=self.device) \
+            if any(m is not None for m in mixes) else None
+        x = streams[0] if streams is not None else \
+            torch.empty((plan.n_rows, s.width), dtype=torch.float32, device=self.device)
         ops.embed(plan.tokens, self.embedding, x, s.embedding_scale)
         ctx = StepContext(plan=plan, cache=cache)
         for i, e in enumerate(s.schedule):
             ctx.entry = i
             ctx.owns_cache = e.cache_from is None
             ctx.kv_entry = i if e.cache_from is None else e.cache_from
+            block, mix = self.blocks[e.layer], mixes[i]
             # the next entry's first norm can ride on this entry's last product
-            nxt = self.blocks[s.schedule[i + 1].layer] if i + 1 < len(s.schedule) else None
-            ctx.after_block_norm = nxt.input_norm() if nxt is not None else None
+            nxt = self.blocks[s.schedule[i + 1].layer] if i + 1 < n else None
+            next_norm = nxt.input_norm() if nxt is not None else None
+            ctx.after_block_norm = next_norm if mix is None else None
             # ... and its first weights can be asked into L2 meanwhile, if it would ask late
-            ctx.after_block_weights = nxt.first_weights(plan.n_rows) if nxt is not None else None
+            ctx.after_block_weights = nxt.first_weights(plan.n_rows) if nxt is not None and mix is None else None
+            if streams is not None:
+                if getattr(block, "writes_block_out", False):
+                    ctx.block_out = streams[i + 1]
+                elif x.data_ptr() == streams[i].data_ptr():
+                    x = ops.depth_mix(streams[i:i + 1], 1, self._one(), torch.empty_like(x))   # the block may overwrite its input
             with ops.trace_range(f"entry {i} (layer {e.layer})"):
-                x = self.blocks[e.layer].forward(x, ctx)
+                x = block.forward(x, ctx)
+            ctx.block_out = None
+            if streams is None:
+                continue
+            if x.data_ptr() != streams[i + 1].data_ptr():
+                ops.depth_mix(x.unsqueeze(0), 1, self._one(), streams[i + 1])
+                x = streams[i + 1]
+            if mix is not None:
+                x = self._mix(mix, streams, ctx, next_norm)
         if plan.n_want == 0:
             return None
         hn = self.final_norm.forward(x, self.dtype, rows=plan.want_rows)
         logits = torch.empty((plan.n_want, s.vocab), dtype=torch.float32, device=self.device)
         ops.linear(hn, self.head, logits)
         return ops.softcap(logits, s.logit_cap) if s.logit_cap > 0.0 else logits
+
+
+    def _one(self):
+        if getattr(self, "_one_coef", None) is None:
+            self._one_coef = torch.ones(1, dtype=torch.float32, device=self.device)
+        return self._one_coef
+
+    def _mix(self, mix, streams, ctx, next_norm):
+        """What a depth mix hands on; the next entry's first norm is written with it when that
+        is a plain RMS norm."""
+        out = torch.empty(streams.shape[1:], dtype=torch.float32, device=self.device)
+        rms = next_norm.as_rms() if next_norm is not None else None
+        if rms is None:
+            return mix.forward(streams, out)
+        normed = torch.empty(out.shape, dtype=self.dtype, device=self.device)
+        mix.forward(streams, out, (rms[0], rms[1], normed))
+        ctx.keep_normed(next_norm, out, normed)
+        return out
 
 
 def tensor_requests(spec: ModelSpec) -> list[TensorRequest]:

@@ -579,3 +579,123 @@ def random_normal(out: torch.Tensor, key0: int, key1: int, mean: float, std: flo
                                   ctypes.c_float(mean), ctypes.c_float(std), _stream()),
            "random_normal")
     return out
+
+
+# ---------------------------------------------------------------------- residual-stream rows
+def _next_norm_args(next_norm, width, rows):
+    """(weight, dtype, eps, out, dtype) of the optional norm of a finished row."""
+    if next_norm is None:
+        return _ptr(None), 0, ctypes.c_float(0.0), _ptr(None), 0
+    w, eps, normed = next_norm
+    assert w.numel() == width and tuple(normed.shape) == (rows, width)
+    return _ptr(w), _code(w.dtype), ctypes.c_float(eps), _ptr(normed), _code(normed.dtype)
+
+
+def norm_add(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+             next_norm: tuple | None = None) -> torch.Tensor:
+    """out = x + y / sqrt(mean(y^2) + eps) * weight, row by row in float32 (out may be x).
+    `next_norm` = (weight, eps, normed) also writes the RMS norm of the finished rows."""
+    rows, width = y.shape
+    assert y.dtype == x.dtype == out.dtype == torch.float32 and x.shape == y.shape == out.shape
+    assert weight.numel() == width
+    _check(lib().sb_norm_add(_ptr(y), _ptr(x), rows, width, _ptr(weight), _code(weight.dtype),
+                             ctypes.c_float(eps), _ptr(out), *_next_norm_args(next_norm, width, rows),
+                             _stream()), "norm_add")
+    return out
+
+
+def depth_mix(planes: torch.Tensor, n_inputs: int, coef: torch.Tensor, out: torch.Tensor,
+              next_norm: tuple | None = None) -> torch.Tensor:
+    """out = sum_j coef[j] * planes[j] over the first n_inputs planes of float32 [n, rows, width]."""
+    rows, width = out.shape
+    assert planes.dtype == out.dtype == torch.float32 and planes.dim() == 3
+    assert tuple(planes.shape[1:]) == (rows, width) and 1 <= n_inputs <= planes.shape[0]
+    assert coef.numel() == n_inputs
+    _check(lib().sb_depth_mix(_ptr(planes), ctypes.c_size_t(rows * width), n_inputs, _ptr(coef),
+                              _code(coef.dtype), rows, width, _ptr(out),
+                              *_next_norm_args(next_norm, width, rows), _stream()), "depth_mix")
+    return out
+
+
+def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float, out: torch.Tensor) -> torch.Tensor:
+    """out = a * sigmoid(slope a) * (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit);
+    gate_up is float32 [rows, 2 ff] = [gate | up]."""
+    rows, ff = out.shape
+    assert gate_up.dtype == torch.float32 and tuple(gate_up.shape) == (rows, 2 * ff)
+    _check(lib().sb_glu_clamped(_ptr(gate_up), rows, ff, ctypes.c_float(limit), ctypes.c_float(slope),
+                                _ptr(out), _code(out.dtype), _stream()), "glu_clamped")
+    return out
+
+
+# ---------------------------------------------------------------------- attention over a latent
+def latent_prep(proj: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, rotary_dim: int,
+                inv_freq: torch.Tensor, row_seq, row_pos, page_off, page_ids, page_size: int,
+                cnorm: torch.Tensor | None, eps: float, cache: torch.Tensor | None,
+                q_wide: torch.Tensor) -> torch.Tensor:
+    """Finishes the fused projection rows [heads x (dim | rot_dim) | rank | rot_dim] (the last two
+    only when `cache` is given): rotation in interleaved pairs, the latent's RMS norm, the cache
+    write (key plane [latent | key part], value plane [latent | 0]), and every head's rotated
+    part into q_wide[:, :, rank:]."""
+    n = proj.shape[0]
+    has_kv = cache is not None
+    assert proj.dtype == torch.float32
+    assert proj.shape[1] == n_heads * (dim + rot_dim) + ((rank + rot_dim) if has_kv else 0)
+    assert tuple(q_wide.shape) == (n, n_heads, rank + rot_dim)
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rotary_dim // 2)
+    _check(lib().sb_latent_prep(
+        _ptr(proj), n, n_heads, dim, rot_dim, rank, rotary_dim, _ptr(inv_freq),
+        _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+        _i32(page_off, "page_off") if has_kv else _ptr(None),
+        _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size,
+        _ptr(cnorm) if has_kv else _ptr(None), _code(cnorm.dtype) if has_kv else 0, ctypes.c_float(eps),
+        _ptr(cache), _code(cache.dtype) if has_kv else 0, _ptr(q_wide), _code(q_wide.dtype),
+        1 if has_kv else 0, _stream()), "latent_prep")
+    return q_wide
+
+
+def head_linear(x: torch.Tensor, x_offset: int, x_row: int, x_head: int, w: torch.Tensor, out: torch.Tensor,
+                out_offset: int, out_row: int, out_head: int, n_rows: int) -> torch.Tensor:
+    """out[r, h, :N] = w[h] @ x[r, h, :K] for w [heads, N, K]; x and out are addressed by element
+    offsets: row r, head h starts at offset + r * row + h * head."""
+    heads, N, K = w.shape
+    assert x.is_contiguous() and out.is_contiguous() and w.is_contiguous()
+    assert x_offset + (n_rows - 1) * x_row + (heads - 1) * x_head + K <= x.numel()
+    assert out_offset + (n_rows - 1) * out_row + (heads - 1) * out_head + N <= out.numel()
+    _check(lib().sb_head_linear(x.data_ptr() + x_offset * x.element_size(), _code(x.dtype),
+                                ctypes.c_size_t(x_row), ctypes.c_size_t(x_head), _ptr(w), _code(w.dtype),
+                                n_rows, heads, N, K, out.data_ptr() + out_offset * out.element_size(),
+                                _code(out.dtype), ctypes.c_size_t(out_row), ctypes.c_size_t(out_head),
+                                _stream()), "head_linear")
+    return out
+
+
+# ---------------------------------------------------------------------- matrix-memory recurrence
+def mlstm_scan(proj: torch.Tensor, plan, n_heads: int, dim: int, vdim: int, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor,
+               num: torch.Tensor, m_row: torch.Tensor) -> torch.Tensor:
+    """Walks every sequence's rows of the step through the recurrence, from and to the state
+    rows of the sequences' slots (float32 [slots, heads, dim + 1, vdim + 1])."""
+    rows = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.shape[1] == 2 * n_heads * (dim + vdim + 1)
+    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (n_heads, dim + 1, vdim + 1)
+    assert num.dtype == torch.float32 and tuple(num.shape) == (rows, n_heads, vdim + 1)
+    assert m_row.dtype == torch.float32 and tuple(m_row.shape) == (rows, n_heads)
+    assert i_bias.dtype == f_bias.dtype and i_bias.numel() == f_bias.numel() == n_heads
+    _check(lib().sb_mlstm_scan(_ptr(proj), plan.n_seqs, _i32(plan.seq_row0, "seq_row0"),
+                               _i32(plan.seq_slot, "seq_slot"), n_heads, dim, vdim, _ptr(i_bias),
+                               _ptr(f_bias), _code(i_bias.dtype), ctypes.c_float(cap),
+                               ctypes.c_float(q_scale), _ptr(state), _ptr(num), _ptr(m_row), _stream()),
+           "mlstm_scan")
+    return num
+
+
+def mlstm_out(num: torch.Tensor, m_row: torch.Tensor, proj: torch.Tensor, n_heads: int, dim: int,
+              vdim: int, norm_w: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """The recurrence's outputs: division by the normalizer, RMS norm per head, the norm's weight
+    and the gate sigmoid(g) of the projection row; out [rows, heads * vdim]."""
+    rows = proj.shape[0]
+    assert tuple(out.shape) == (rows, n_heads * vdim) and norm_w.numel() == n_heads * vdim
+    _check(lib().sb_mlstm_out(_ptr(num), _ptr(m_row), _ptr(proj), rows, n_heads, dim, vdim, _ptr(norm_w),
+                              _code(norm_w.dtype), ctypes.c_float(eps), _ptr(out), _code(out.dtype),
+                              _stream()), "mlstm_out")
+    return out

@@ -50,6 +50,7 @@ class StepContext:
     next_weights: Optional[torch.Tensor] = None         # an L2 hint for the running part's last product
     after_block_weights: Optional[torch.Tensor] = None  # what the entry that runs next streams first, if it asks late
     _normed: Optional[tuple] = None        # (norm, rows, normed rows) of the last `linear` that had one
+    block_out: Optional[torch.Tensor] = None            # where the caller wants the running block's result (a block may ignore it)
 
     def linear(self, a, w, out, epilogue, residual=None, bias=None, act_dtype=None):
         """ops.linear into float32 `out`; when `next_norm` is an RMS norm with a plain weight,
@@ -65,6 +66,10 @@ class StepContext:
                    warm=warm)
         self._normed = (norm, out, normed)
         return out
+
+    def keep_normed(self, norm, x, normed) -> None:
+        """Leaves `normed` = norm(x) behind for the part that applies `norm` to `x` next."""
+        self._normed = (norm, x, normed)
 
     def take_normed(self, norm, x) -> Optional[torch.Tensor]:
         """`norm` of the rows `x`, if the part that just ran left it behind; else None."""
@@ -165,6 +170,7 @@ POSITION_ENCODINGS: dict[str, type] = {}
 MIXERS: dict[str, type] = {}
 FEED_FORWARDS: dict[str, type] = {}
 BLOCKS: dict[str, type] = {}
+DEPTH_MIXES: dict[str, type] = {}
 
 
 def _register(table, what):
@@ -182,6 +188,7 @@ register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_mixer = _register(MIXERS, "mixer")
 register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
 register_block = _register(BLOCKS, "block arrangement")
+register_depth_mix = _register(DEPTH_MIXES, "depth mix")
 
 
 def make(table: dict, what: str, spec, dtype, device):

@@ -47,3 +47,79 @@ class PreNormBlock(Block):
         # the block's result is the feed-forward's, so what follows the block follows its product
         ctx.next_norm, ctx.next_weights = ctx.after_block_norm, ctx.after_block_weights
         return self.feed_forward.forward(f, ctx, residual=x)
+
+
+@register_block("sandwich_norm")
+class SandwichNormBlock(Block):
+    """Norm before and after each sublayer: x1 = x + post1(mix(pre1(x))); x2 = x1 + post2(ffn(pre2(x1)))
+    (without a feed-forward the block's result is x1).  The normed sublayer result joins the
+    stream in one kernel (`ops.norm_add`), which also writes the norm that comes next when that is
+    known: the feed-forward's own input norm, or the next entry's first norm
+    (`ctx.after_block_norm`).  When the caller names a place for the result (`ctx.block_out`), the
+    block writes there and leaves its input as it was; else it overwrites its input."""
+    writes_block_out = True
+
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        self.dtype = dtype
+        if spec.mixer_post_norm is None:
+            raise ConfigError("a sandwich_norm block needs mixer_post_norm")
+        if spec.feed_forward is not None and (spec.feed_forward_norm is None or spec.feed_forward_post_norm is None):
+            raise ConfigError("a sandwich_norm block with a feed-forward needs both of its norms")
+        self.mixer_norm = make(NORMS, "norm", spec.mixer_norm, dtype, device)
+        self.mixer = make(MIXERS, "mixer", spec.mixer, dtype, device)
+        self.mixer_post_norm = make(NORMS, "norm", spec.mixer_post_norm, dtype, device)
+        self.parts = [self.mixer_norm, self.mixer, self.mixer_post_norm]
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward_norm = make(NORMS, "norm", spec.feed_forward_norm, dtype, device)
+            self.feed_forward = make(FEED_FORWARDS, "feed-forward", spec.feed_forward, dtype, device)
+            self.feed_forward_post_norm = make(NORMS, "norm", spec.feed_forward_post_norm, dtype, device)
+            self.parts += [self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm]
+
+    def tensor_requests(self):
+        return [r for p in self.parts for r in p.tensor_requests()]
+
+    def bind(self, get):
+        for p in self.parts:
+            p.bind(get)
+
+    def kv_need(self):
+        return self.mixer.kv_need()
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def input_norm(self):
+        return self.mixer_norm
+
+    def _join(self, y, x, post, out, ctx, then):
+        """out = x + post(y); the norm `then` of the result rides along when it is a plain RMS norm."""
+        import torch
+        from .. import ops
+        w, eps = post.as_rms()
+        rms = then.as_rms() if then is not None else None
+        if rms is None:
+            return ops.norm_add(y, x, w, eps, out)
+        normed = torch.empty(out.shape, dtype=self.dtype, device=out.device)
+        ops.norm_add(y, x, w, eps, out, (rms[0], rms[1], normed))
+        ctx.keep_normed(then, out, normed)
+        return out
+
+    def forward(self, x, ctx):
+        out, ctx.block_out = (ctx.block_out if ctx.block_out is not None else x), None
+        after, ctx.after_block_norm, ctx.after_block_weights = ctx.after_block_norm, None, None
+        h = ctx.take_normed(self.mixer_norm, x)
+        if h is None:
+            h = self.mixer_norm.forward(x, self.dtype)
+        ctx.next_norm = ctx.next_weights = None      # the post norm, not a norm of the stream, follows the product
+        y = self.mixer.forward(h, ctx)
+        if self.feed_forward is None:
+            return self._join(y, x, self.mixer_post_norm, out, ctx, after)
+        x1 = self._join(y, x, self.mixer_post_norm, out, ctx, self.feed_forward_norm)
+        f = ctx.take_normed(self.feed_forward_norm, x1)
+        if f is None:
+            f = self.feed_forward_norm.forward(x1, self.dtype)
+        ctx.next_norm = ctx.next_weights = None
+        y = self.feed_forward.forward(f, ctx)
+        return self._join(y, x1, self.feed_forward_post_norm, out, ctx, after)

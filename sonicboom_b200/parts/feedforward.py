@@ -56,3 +56,48 @@ class SwiGLU(FeedForward):
         return ctx.linear(t, self.w_down, out,
                           ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
                           residual=residual, act_dtype=self.dtype)
+
+
+@register_feed_forward("glu_clamped")
+class ClampedGLU(FeedForward):
+    """Gated feed-forward with clamped factors: g = min(Wgate h, limit), u = clamp(Wup h, -limit,
+    limit), y = Wdown (g * sigmoid(slope g) * (u + 1)), no biases.  `params` gives `limit`,
+    `slope` and optionally `names`, the tensor names of the three matrices after the prefix.
+    Gate and up are one product over [gate rows | up rows]; its float32 rows go through the
+    activation kernel, which writes the activation dtype once."""
+
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        self.spec, self.dtype = spec, dtype
+        p = dict(spec.params)
+        self.limit, self.slope = float(p.get("limit", 0.0)), float(p.get("slope", 1.0))
+        if not self.limit > 0.0:
+            raise ConfigError(f"feed-forward limit {self.limit} must be positive")
+        self.names = tuple(p.get("names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+        self.w_gate_up = self.w_down = None
+
+    def tensor_requests(self):
+        p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
+        g, u, dn = self.names
+        return [TensorRequest(p + g, (ff, d)), TensorRequest(p + u, (ff, d)), TensorRequest(p + dn, (d, ff))]
+
+    def bind(self, get):
+        p = self.spec.prefix
+        g, u, dn = self.names
+        gate, up = get(p + g), get(p + u)
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.w_down = get(p + dn)
+
+    def forward(self, h, ctx, residual=None):
+        rows, ff = h.shape[0], self.spec.intermediate
+        gu = torch.empty((rows, 2 * ff), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_gate_up, gu)
+        t = torch.empty((rows, ff), dtype=self.dtype, device=h.device)
+        ops.glu_clamped(gu, self.limit, self.slope, t)
+        out = residual if residual is not None else \
+            torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
+        return ctx.linear(t, self.w_down, out,
+                          ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
+                          residual=residual, act_dtype=self.dtype)

@@ -1,0 +1,111 @@
+"""Attention over a cached low-rank latent.
+
+Per token the mixer projects its input to queries (per head `dim` unrotated and `rot_dim`
+rotated dimensions, laid out head by head as [dim | rot_dim]) and to rank + rot_dim numbers: the
+first `rank`, RMS-normed with a plain weight, are the latent c; the last rot_dim are one rotated
+key part kr that all heads share.  Only c and kr are cached.  Head h's key is [Uk_h c | kr], its
+value Uv_h c, the score (q . Uk_h c + qr . kr) * scale over a sliding window, softmax, then the
+output projection over the concatenated heads.
+
+Computed in the absorbed form, which needs nothing but the cache whatever the step brings
+(a prompt, a portion of one, a single token):
+    q~_h = Uk_h^T q_h                     (`ops.head_linear`, a product per head)
+    s    = ([q~_h | qr_h] . [c | kr]) * scale  and  z_h = softmax(s) C   (the paged attention kernels on
+                                           a cache entry with ONE head of size rank + rot_dim)
+    o_h  = Uv_h z_h                        (`ops.head_linear`)
+so the framework's attention kernels (plain float32, mma.sync, tcgen05) run unchanged.  A mixer
+that reads another entry's cache (`ScheduleEntry.cache_from`) projects queries only and uses
+that entry's c and kr as the cache holds them, with its own Uk, Uv, window and scale.
+
+Tensors after the prefix: q [heads*(dim+rot_dim), width], dkv [rank+rot_dim, width], dkv.norm
+[rank], uk [heads*dim, rank], uv [heads*vdim, rank], o [width, heads*vdim].
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.kv import KVNeed
+from ..weights.loader import TensorRequest
+from .base import POSITION_ENCODINGS, Mixer, make, register_mixer
+
+
+@register_mixer("latent_attention")
+class LatentAttention(Mixer):
+    def __init__(self, spec, dtype, device):
+        from ..config.specs import ConfigError
+        self.spec, self.dtype, self.device = spec, dtype, device
+        p = dict(spec.params)
+        self.h, self.dim = spec.n_heads, spec.head_dim
+        try:
+            self.rd, self.vd, self.rank = int(p["rot_dim"]), int(p["vdim"]), int(p["kv_rank"])
+        except KeyError as e:
+            raise ConfigError(f"latent attention needs the parameter {e.args[0]}") from None
+        self.eps = float(p.get("eps", 1e-6))
+        self.keep = int(p.get("keep", spec.window))      # what the cache entry must keep (0: everything)
+        if spec.window and self.keep and self.keep < spec.window:
+            raise ConfigError(f"a cache entry that keeps {self.keep} keys cannot serve a window of {spec.window}")
+        self.own_kv = bool(p.get("own_kv", True))        # False: it only ever reads another entry's cache
+        self.wide = self.rank + self.rd
+        self.position = make(POSITION_ENCODINGS, "position encoding", spec.position, dtype, device)
+        if getattr(self.position, "layout", None) != "interleaved" and self.position.rotary_dim:
+            raise ConfigError("latent attention rotates interleaved pairs; position encoding "
+                              f"{spec.position.kind!r} pairs otherwise")
+        if self.position.rotary_dim > self.rd:
+            raise ConfigError(f"{self.position.rotary_dim} rotated dimensions exceed rot_dim {self.rd}")
+        self.w_in = self.cnorm = self.w_ukt = self.w_uv = self.w_o = None
+
+    def kv_need(self):
+        return KVNeed(1, self.wide, self.keep)
+
+    def tensor_requests(self):
+        p, d = self.spec.prefix, self.spec.width
+        own = [TensorRequest(p + "dkv", (self.wide, d)),
+               TensorRequest(p + "dkv.norm", (self.rank,), "norm")] if self.own_kv else []
+        return [TensorRequest(p + "q", (self.h * (self.dim + self.rd), d))] + own + [
+                TensorRequest(p + "uk", (self.h * self.dim, self.rank)),
+                TensorRequest(p + "uv", (self.h * self.vd, self.rank)),
+                TensorRequest(p + "o", (d, self.h * self.vd))]
+
+    def bind(self, get):
+        p = self.spec.prefix
+        q = get(p + "q")
+        if self.own_kv:
+            dkv = get(p + "dkv")
+            if dkv.dtype != q.dtype:
+                q, dkv = q.float(), dkv.float()
+            self.w_in = torch.cat([q, dkv], dim=0).contiguous()
+            self.cnorm = get(p + "dkv.norm")
+        else:
+            self.w_in = q
+        # Uk as [head, rank, dim]: the product per head maps a head's dim query values to rank
+        self.w_ukt = get(p + "uk").view(self.h, self.dim, self.rank).transpose(1, 2).contiguous()
+        self.w_uv = get(p + "uv").view(self.h, self.vd, self.rank).contiguous()
+        self.w_o = get(p + "o")
+
+    def forward(self, h, ctx, residual=None):
+        rows, plan = h.shape[0], ctx.plan
+        owns = ctx.owns_cache
+        if owns and not self.own_kv:
+            raise ops.KernelError("this latent attention has no key/value projection of its own: "
+                                  "its schedule entry must read another entry's cache")
+        hw = self.dim + self.rd
+        n_in = self.h * hw + (self.wide if owns else 0)
+        proj = torch.empty((rows, n_in), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_in[:n_in], proj)
+        storage = ctx.kv_storage()
+        g = plan.groups[ctx.kv_group()]
+        q_wide = torch.empty((rows, self.h, self.wide), dtype=self.dtype, device=h.device)
+        ops.latent_prep(proj, self.h, self.dim, self.rd, self.rank, self.position.rotary_dim,
+                        self.position.inv_freq, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
+                        g.page_size, self.cnorm, self.eps, storage if owns else None, q_wide)
+        ops.head_linear(proj, 0, n_in, hw, self.w_ukt, q_wide, 0, self.h * self.wide, self.wide, rows)
+        z = torch.empty((rows, self.h * self.wide), dtype=self.dtype, device=h.device)
+        ops.attention(q_wide, z, plan, ctx.kv_group(), storage, self.h, 1, self.wide,
+                      self.spec.window, self.spec.scale)
+        mixed = torch.empty((rows, self.h * self.vd), dtype=self.dtype, device=h.device)
+        ops.head_linear(z, 0, self.h * self.wide, self.wide, self.w_uv, mixed, 0, self.h * self.vd, self.vd, rows)
+        out = residual if residual is not None else \
+            torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
+        return ctx.linear(mixed, self.w_o, out, ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
+                          residual=residual, act_dtype=self.dtype)

@@ -28,3 +28,17 @@ class RMSNorm(Norm):
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
         return ops.rmsnorm(x, self.weight, self.eps, out, rows)
+
+
+@register_norm("rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """RMS norm whose weight is one number for all coordinates: y = x / sqrt(mean(x^2) + eps) * g.
+    The stored tensor has shape []; bound, it is spread over the width, so every kernel that
+    takes an RMS norm's weight vector (the norm kernel itself, and the kernels that norm a row
+    they have just finished) serves it unchanged."""
+
+    def tensor_requests(self):
+        return [TensorRequest(self.tensor, (), "norm")]
+
+    def bind(self, get):
+        self.weight = get(self.tensor).reshape(1).expand(self.width).contiguous()

@@ -36,3 +36,24 @@ class NoPosition(PositionEncoding):
     def __init__(self, spec, dtype, device):
         self.head_dim, self.rotary_dim = spec.head_dim, 0
         self.inv_freq = torch.zeros(1, dtype=torch.float32, device=device)
+
+
+@register_position_encoding("rope_interleaved")
+class RotaryInterleaved(PositionEncoding):
+    """Rotation of neighbouring pairs: elements 2i and 2i + 1 of the rotated vector turn by
+    position * base^(-2i / rotary_dim), i < rotary_dim / 2; elements from rotary_dim on pass
+    unchanged.  `head_dim` is the length of the rotated vector (a head's rotated part).  The
+    frequency table is worked out in double precision and rounded once; the kernels that pair
+    elements this way (`ops.latent_prep`) take the angle as float32 position * table entry."""
+    layout = "interleaved"
+
+    def __init__(self, spec, dtype, device):
+        self.head_dim = spec.head_dim
+        self.rotary_dim = spec.rotary_dim or spec.head_dim
+        if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
+            from ..config.specs import ConfigError
+            raise ConfigError(f"rotary_dim {self.rotary_dim} must be even and at most the rotated "
+                              f"vector's length {self.head_dim}")
+        i = np.arange(max(1, self.rotary_dim // 2), dtype=np.float64)
+        inv = np.power(np.float64(spec.theta), -2.0 * i / np.float64(self.rotary_dim))
+        self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
