@@ -394,6 +394,204 @@ def run(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- --arch zolulix
+def zolulix_config(width, n_layers, ff, vocab, heads, dim, rot_dim, vdim, rank, window, r_heads, r_dim, r_vdim):
+    """A Zolulix model of the given layer sizes: recurrence and attention layers alternate, every
+    second attention layer reads the cache of the one before it."""
+    layers, owner = [], None
+    for i in range(n_layers):
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+        if i % 2 == 0:
+            layers.append({"type": "mlstm", "mlp": mlp,
+                           "mixer": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "gate_cap": 15.0}})
+            continue
+        m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": rank,
+             "scale": (dim + rot_dim) ** -0.5, "mask": {"size": window}, "rot": {"base": 250000.0, "dims": rot_dim}}
+        if owner is not None:
+            m["kv_from"], owner = owner, None
+        else:
+            owner = i
+        layers.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Zolulix", "vocab": vocab, "width": width, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "layers": layers}
+
+
+ZOLULIX_SIZES = {
+    # name: (Zolulix sizes, the Qwen2.5 configuration of equal width, layers, feed-forward and vocabulary)
+    "w2048": (dict(width=2048, n_layers=8, ff=8192, vocab=32768, heads=16, dim=64, rot_dim=32, vdim=64, rank=96,
+                   window=1024, r_heads=4, r_dim=128, r_vdim=512),
+              dict(QWEN25_7B, hidden_size=2048, num_hidden_layers=8, num_attention_heads=16,
+                   num_key_value_heads=2, intermediate_size=8192, vocab_size=32768)),
+    "w3584": (dict(width=3584, n_layers=8, ff=18944, vocab=32768, heads=28, dim=96, rot_dim=32, vdim=128, rank=224,
+                   window=4096, r_heads=8, r_dim=128, r_vdim=448),
+              dict(QWEN25_7B, num_hidden_layers=8, vocab_size=32768)),
+}
+
+
+def run_zolulix(args) -> int:
+    """Prefill and decode throughput of Zolulix models at layer sizes of real models (random
+    weights), beside the Qwen2.5 decoder of equal width, depth, feed-forward and vocabulary; and
+    each new kernel alone with the bytes it must move, beside the like kernel of that decoder."""
+    import torch
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+    from sonicboom_b200.engine.decode import DecodeLoop
+
+    torch.cuda.set_device(0)
+    dev, pk = "cuda:0", peaks()
+    gen = torch.Generator().manual_seed(1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than L2
+
+    def timed(fn, reps=5):
+        """Median device time (ms) of fn(), L2 flushed before every timed call, after 3 warm-up calls."""
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    def model_points(m, n_prompt, batch, steps, warmup):
+        vocab = m.spec.vocab
+        engine = sb.Engine(m, max_tokens=max(n_prompt, batch * (n_prompt + warmup + 2 * steps + 64)), n_slots=batch)
+        p = torch.randint(0, vocab, (n_prompt,), generator=gen).tolist()
+
+        def prefill():
+            s = engine.open()
+            engine.step([(s, p, [n_prompt - 1])])
+            engine.close(s)
+        pre_ms = timed(prefill, 3)
+        slots = [engine.open() for _ in range(batch)]
+        first = []
+        for i in range(0, batch, 8):
+            lg = engine.step([(s, p, [n_prompt - 1]) for s in slots[i:i + 8]])
+            first += lg.argmax(dim=-1).tolist()
+        loop = DecodeLoop(engine, slots, warmup + 2 * steps + 2)
+        loop.run_device(first, warmup)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        loop.run_device(None, steps)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        launches = loop.launches_per_step
+        loop.close()
+        for s in slots:
+            engine.close(s)
+        del engine, loop
+        torch.cuda.empty_cache()
+        return {"prefill_tokens": n_prompt, "prefill_ms": round(pre_ms, 3),
+                "prefill_tok_s": round(n_prompt / (pre_ms / 1e3), 1), "decode_batch": batch,
+                "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1),
+                "decode_launches_per_step": launches, "weight_bytes": weight_bytes(m)}
+
+    def kernels(z, rows):
+        """Each new kernel alone at `rows` rows with its algorithmic bytes (what it must read and
+        write once), and the decoder's like kernels (norm, rotation + cache write)."""
+        W, ff = z["width"], z["ff"]
+        f32, bf = torch.float32, torch.bfloat16
+        out = {}
+
+        def rec(name, ms, nbytes, flops=0):
+            out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
+                         "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+            if flops:
+                out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+        x, y = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+        w = torch.ones(W, device=dev, dtype=bf)
+        o, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
+        rec("rmsnorm (decoder's)", timed(lambda: ops.rmsnorm(x, w, 1e-5, nb)), rows * W * 6)
+        rec("norm_add + next norm", timed(lambda: ops.norm_add(y, x, w, 1e-5, o, (w, 1e-5, nb))), rows * W * 14)
+        n_in = z["n_layers"] // 2 + 1
+        planes = torch.randn(n_in, rows, W, device=dev)
+        coef = torch.ones(n_in, device=dev, dtype=bf)
+        rec(f"depth_mix of {n_in} + next norm", timed(lambda: ops.depth_mix(planes, n_in, coef, o, (w, 1e-5, nb))),
+            rows * W * (4 * n_in + 6))
+        gu, t = torch.randn(rows, 2 * ff, device=dev), torch.empty(rows, ff, device=dev, dtype=bf)
+        rec("glu_clamped", timed(lambda: ops.glu_clamped(gu, 7.0, 1.702, t)), rows * ff * 10)
+        H, dim, rd, vd, rank = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["rank"]
+        wide = rank + rd
+        proj = torch.randn(rows, H * (dim + rd) + wide, device=dev)
+        cache = torch.zeros((rows + 63) // 64, 2, 1, 64, wide, device=dev, dtype=bf)
+        q_wide = torch.empty(rows, H, wide, device=dev, dtype=bf)
+        inv = torch.ones(rd // 2, device=dev)
+        row_seq = torch.zeros(rows, dtype=torch.int32, device=dev)
+        row_pos = torch.arange(rows, dtype=torch.int32, device=dev)
+        page_off = torch.tensor([0, cache.shape[0]], dtype=torch.int32, device=dev)
+        page_ids = torch.arange(cache.shape[0], dtype=torch.int32, device=dev)
+        cn = torch.ones(rank, device=dev, dtype=bf)
+        rec("latent_prep", timed(lambda: ops.latent_prep(proj, H, dim, rd, rank, rd, inv, row_seq, row_pos, page_off,
+                                                         page_ids, 64, cn, 1e-5, cache, q_wide)),
+            rows * (4 * (H * rd + wide) + 2 * H * rd + 4 * wide))
+        hq, hkv, hd = 28, 4, 128
+        qkv = torch.randn(rows, (hq + 2 * hkv) * hd, device=dev)
+        cache2 = torch.zeros((rows + 63) // 64, 2, hkv, 64, hd, device=dev, dtype=bf)
+        q2 = torch.empty(rows, hq, hd, device=dev, dtype=bf)
+        inv2 = torch.ones(hd // 2, device=dev)
+        rec("rope_store (decoder's)", timed(lambda: ops.rope_store(qkv, hq, hkv, hd, hd, inv2, row_seq, row_pos, page_off,
+                                                                    page_ids, 64, cache2, q2)),
+            rows * (hq + 2 * hkv) * hd * 6)
+        ukt = torch.randn(H, rank, dim, device=dev).to(bf)
+        uv = torch.randn(H, vd, rank, device=dev).to(bf)
+        zz = torch.randn(rows, H * wide, device=dev).to(bf)
+        mixed = torch.empty(rows, H * vd, device=dev, dtype=bf)
+        rec("head_linear (queries to latent)",
+            timed(lambda: ops.head_linear(proj, 0, proj.shape[1], dim + rd, ukt, q_wide, 0, H * wide, wide, rows)),
+            rows * H * (4 * dim + 2 * rank) + 2 * H * rank * dim, 2 * rows * H * dim * rank)
+        rec("head_linear (latent to values)",
+            timed(lambda: ops.head_linear(zz, 0, H * wide, wide, uv, mixed, 0, H * vd, vd, rows)),
+            rows * H * (2 * rank + 2 * vd) + 2 * H * rank * vd, 2 * rows * H * vd * rank)
+        rh, rdim, rvd = z["r_heads"], z["r_dim"], z["r_vdim"]
+
+        class Plan:
+            n_seqs = 1 if rows > 64 else rows
+        per = rows // Plan.n_seqs
+        Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
+        Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
+        rproj = torch.randn(rows, 2 * rh * (rdim + rvd + 1), device=dev) * 0.1
+        state = torch.zeros(Plan.n_seqs, rh, rvd + 1, rdim + 1, device=dev)
+        num, m_row = torch.empty(rows, rh, rvd + 1, device=dev), torch.empty(rows, rh, device=dev)
+        bi = torch.zeros(rh, device=dev, dtype=bf)
+        rec(f"mlstm_scan ({Plan.n_seqs} sequence(s) of {per})",
+            timed(lambda: ops.mlstm_scan(rproj, Plan, rh, rdim, rvd, bi, bi, 15.0, rdim ** -0.5, state, num, m_row)),
+            rows * rh * 4 * (2 * rdim + 2 * rvd + 3) + 8 * state.numel(), 4 * rows * rh * rdim * (rvd + 1))
+        ro = torch.empty(rows, rh * rvd, device=dev, dtype=bf)
+        nw = torch.ones(rh * rvd, device=dev, dtype=bf)
+        rec("mlstm_out", timed(lambda: ops.mlstm_out(num, m_row, rproj, rh, rdim, rvd, nw, 1e-5, ro)),
+            rows * rh * rvd * 10)
+        return out
+
+    result = {"arch": "zolulix", "impl": "ours", "dtype": "bf16", "peaks": pk, "sizes": {},
+              "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+              "timing": "CUDA events; kernels alone: median of 5 after 3 warm-up calls, L2 flushed "
+                        "(256 MB written) before each; models: prefill median of 3, decode one region of K steps"}
+    with ClockSampler() as clocks:
+        for name, (z, q) in ZOLULIX_SIZES.items():
+            if args.sizes and name not in args.sizes.split(","):
+                continue
+            zc = zolulix_config(**z)
+            rec = {"zolulix_config": {k: v for k, v in z.items()}}
+            for label, cfg in (("zolulix", zc), ("qwen2.5 (equal width, layers, ff, vocab)", q)):
+                m = sb.random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+                rec[label] = model_points(m, args.prompt, args.batch, args.steps, args.warmup)
+                del m
+                torch.cuda.empty_cache()
+            rec["kernels_prefill_rows_%d" % args.prompt] = kernels(z, args.prompt)
+            rec["kernels_decode_rows_%d" % args.batch] = kernels(z, args.batch)
+            result["sizes"][name] = rec
+    ops.check_status()
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -413,6 +611,12 @@ def main() -> int:
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--eager", action="store_true",
                     help="with --only decode: launch the step kernel by kernel, not as a graph")
+    ap.add_argument("--arch", choices=["qwen2", "zolulix"], default="qwen2",
+                    help="zolulix: that design's prefill and decode throughput and its kernels alone, "
+                         "beside the Qwen2.5 decoder of equal sizes (its own JSON line; the default "
+                         "workload is unchanged)")
+    ap.add_argument("--sizes", default="", help="with --arch zolulix: which of its sizes to run (comma separated)")
+    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix: prompt length")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -421,6 +625,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.arch == "zolulix":
+        return run_zolulix(args)
     return run(args)
 
 

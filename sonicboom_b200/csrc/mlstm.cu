@@ -10,12 +10,16 @@
 // a bias): i = cap tanh(x_i / cap), f = logsigmoid(cap tanh(x_f / cap)).
 //
 // n is S for a value that is always one, so the state is kept as one matrix of vdim + 1 columns,
-// and the columns are independent of each other: a thread owns a column, walks the step's
-// tokens in order and never meets another thread.  Every column also keeps a copy of m (row
-// `dim` of the state), so that no column ever reads what another one writes.  State per slot:
-// float32 [heads, dim + 1, vdim + 1].  The walk is the recurrence itself, token by token in
-// float32, for prompts, portions of prompts and single tokens alike, so a position's result
-// does not depend on how its sequence was cut into steps.
+// and the columns are independent of each other.  A column's dim values are shared out over DS
+// lanes of a warp (lane s keeps d = s, s + DS, ... in registers), the lanes' partial sums of
+// S_t^T q_t meet by shuffles, and columns never meet: every column also keeps a copy of m, so
+// that no column reads what another one writes.  State per slot: float32 [heads, vdim + 1,
+// dim + 1], a column's dim values side by side and its copy of m after them.  The walk is the
+// recurrence itself, token by token in float32, for prompts, portions of prompts and single
+// tokens alike, so a position's result does not depend on how its sequence was cut into steps.
+// Tokens are staged in shared memory a chunk at a time; per chunk the gates are worked out by a
+// thread per token, the running maximum by one thread in order (an add and a max per token),
+// and the two decay factors again by a thread per token.
 //
 //   sb_mlstm_scan:  numerators S_t^T q_t for all vdim + 1 columns and m_t, per row and head;
 //   sb_mlstm_out:   the division, the RMS norm of each head's output, its weight, the output
@@ -29,96 +33,109 @@
 
 namespace {
 
-constexpr int VB = 64;          // columns (threads) per block
-constexpr int TC = 16;          // tokens staged in shared memory at a time
+constexpr int SCAN_THREADS = 256;
+constexpr int MAX_TC = 32;      // most tokens staged at a time
 
 __device__ __forceinline__ float log_sigmoid(float z) {
   return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
 }
 
-// DIM > 0: the column lives in DIM registers; DIM == 0: any dim, the column lives in shared memory.
-template <int DIM, typename TB>
-__global__ void __launch_bounds__(VB)
+// DS lanes share a column, NPT values of it each (DS * NPT >= dim; values past dim stay zero).
+template <int DS, int NPT, typename TB>
+__global__ void __launch_bounds__(SCAN_THREADS)
 mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int32_t* seq_slot, int H,
-                  int dim_rt, int vdim, const TB* __restrict__ i_bias, const TB* __restrict__ f_bias,
+                  int dim, int vdim, int tc, const TB* __restrict__ i_bias, const TB* __restrict__ f_bias,
                   float cap, float q_scale, float* state, float* num, float* m_row) {
+  constexpr int CPB = SCAN_THREADS / DS;   // columns per block
   extern __shared__ float smem[];
-  const int dim = DIM > 0 ? DIM : dim_rt;
-  float* q_s = smem;                       // [TC][dim]
-  float* k_s = q_s + TC * dim;             // [TC][dim]
-  float* v_s = k_s + TC * dim;             // [TC][VB]
-  float* ig_s = v_s + TC * VB;             // [TC]
-  float* fg_s = ig_s + TC;                 // [TC]
-  float* S_s = fg_s + TC;                  // [dim][VB] when DIM == 0
+  const int dim_p = DS * NPT;
+  float* q_s = smem;                       // [tc][dim_p]
+  float* k_s = q_s + tc * dim_p;           // [tc][dim_p]
+  float* v_s = k_s + tc * dim_p;           // [tc][CPB]
+  float* ig_s = v_s + tc * CPB;            // [tc] log input gate, then its factor exp(i - m)
+  float* fg_s = ig_s + tc;                 // [tc] log forget gate, then its factor exp(f + m' - m)
+  float* m_s = fg_s + tc;                  // [tc + 1]: m before the chunk, then after each token
   sb_pdl_launch();
   const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int jj = blockIdx.z * VB + tid, cols = vdim + 1;
+  const int c = tid / DS, ls = tid % DS;
+  const int jj = blockIdx.z * CPB + c, cols = vdim + 1;
   const bool active = jj < cols;
   const int row0 = seq_row0[b], T = seq_row0[b + 1] - row0;
-  float* st = state + ((size_t)seq_slot[b] * H + h) * (size_t)(dim + 1) * cols;
+  float* st = state + (((size_t)seq_slot[b] * H + h) * cols + (active ? jj : 0)) * (size_t)(dim + 1);
   const float bi = sb_to_f32<TB>(i_bias[h]), bf = sb_to_f32<TB>(f_bias[h]);
   sb_pdl_wait();
-  float S_r[DIM > 0 ? DIM : 1];
-  if (DIM > 0) {
+  float S[NPT];
 #pragma unroll
-    for (int d = 0; d < (DIM > 0 ? DIM : 1); ++d) S_r[d] = active ? st[(size_t)d * cols + jj] : 0.0f;
-  } else {
-    for (int d = 0; d < dim; ++d) S_s[d * VB + tid] = active ? st[(size_t)d * cols + jj] : 0.0f;
+  for (int i = 0; i < NPT; ++i) {
+    const int d = ls + DS * i;
+    S[i] = (active && d < dim) ? st[d] : 0.0f;
   }
-  float m = st[(size_t)dim * cols + (active ? jj : vdim)];
+  if (tid == 0) m_s[0] = st[dim];
   const int q_off = h * dim, k_off = H * dim + h * dim, v_off = 2 * H * dim + h * vdim;
   const int i_off = 2 * H * dim + 2 * H * vdim + h, f_off = i_off + H;
-  for (int t0 = 0; t0 < T; t0 += TC) {
-    const int nt = min(TC, T - t0);
-    __syncthreads();
-    for (int e = tid; e < nt * dim; e += VB) {
-      const float* src = proj + (size_t)(row0 + t0 + e / dim) * ld;
-      q_s[e] = src[q_off + e % dim] * q_scale;
-      k_s[e] = src[k_off + e % dim];
+  float m_last = 0.0f;
+  for (int t0 = 0; t0 < T; t0 += tc) {
+    const int nt = min(tc, T - t0);
+    for (int e = tid; e < nt * dim_p; e += SCAN_THREADS) {
+      const int tt = e / dim_p, d = e % dim_p;
+      const float* src = proj + (size_t)(row0 + t0 + tt) * ld;
+      q_s[e] = d < dim ? src[q_off + d] * q_scale : 0.0f;
+      k_s[e] = d < dim ? src[k_off + d] : 0.0f;
     }
-    for (int tt = 0; tt < nt; ++tt)
-      v_s[tt * VB + tid] = jj < vdim ? proj[(size_t)(row0 + t0 + tt) * ld + v_off + jj] : (jj == vdim ? 1.0f : 0.0f);
+    for (int e = tid; e < nt * CPB; e += SCAN_THREADS) {
+      const int tt = e / CPB, j = blockIdx.z * CPB + e % CPB;
+      v_s[e] = j < vdim ? proj[(size_t)(row0 + t0 + tt) * ld + v_off + j] : (j == vdim ? 1.0f : 0.0f);
+    }
     if (tid < nt) {
       const float* src = proj + (size_t)(row0 + t0 + tid) * ld;
       ig_s[tid] = cap * tanhf((src[i_off] + bi) / cap);
       fg_s[tid] = log_sigmoid(cap * tanhf((src[f_off] + bf) / cap));
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float fm = fg_s[tt] + m, ig = ig_s[tt];
-      const float mn = fmaxf(fm, ig);
-      const float a = expf(fm - mn), bv = expf(ig - mn) * v_s[tt * VB + tid];
-      m = mn;
-      const float* kt = k_s + tt * dim;
-      const float* qt = q_s + tt * dim;
-      float acc = 0.0f;
-      if (DIM > 0) {
-#pragma unroll
-        for (int d = 0; d < (DIM > 0 ? DIM : 1); ++d) {
-          const float s = fmaf(S_r[d], a, kt[d] * bv);
-          S_r[d] = s;
-          acc = fmaf(s, qt[d], acc);
-        }
-      } else {
-        for (int d = 0; d < dim; ++d) {
-          const float s = fmaf(S_s[d * VB + tid], a, kt[d] * bv);
-          S_s[d * VB + tid] = s;
-          acc = fmaf(s, qt[d], acc);
-        }
+    if (tid == 0) {
+      float m = m_s[0];
+      for (int tt = 0; tt < nt; ++tt) {
+        m = fmaxf(fg_s[tt] + m, ig_s[tt]);
+        m_s[tt + 1] = m;
       }
-      const size_t row = (size_t)(row0 + t0 + tt);
-      if (active) num[(row * H + h) * cols + jj] = acc;
-      if (jj == 0) m_row[row * H + h] = mn;
     }
+    __syncthreads();
+    if (tid < nt) {
+      const float mn = m_s[tid + 1];
+      const float keep = expf(fg_s[tid] + m_s[tid] - mn), take = expf(ig_s[tid] - mn);
+      fg_s[tid] = keep;
+      ig_s[tid] = take;
+      if (blockIdx.z == 0) m_row[(size_t)(row0 + t0 + tid) * H + h] = mn;
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float a = fg_s[tt], bv = ig_s[tt] * v_s[tt * CPB + c];
+      const float* kt = k_s + tt * dim_p + ls;
+      const float* qt = q_s + tt * dim_p + ls;
+      float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const float sv = fmaf(S[i], a, kt[DS * i] * bv);
+        S[i] = sv;
+        if (i & 1) acc1 = fmaf(sv, qt[DS * i], acc1);
+        else acc0 = fmaf(sv, qt[DS * i], acc0);
+      }
+      float acc = acc0 + acc1;
+#pragma unroll
+      for (int o = DS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (active && ls == 0) num[((size_t)(row0 + t0 + tt) * H + h) * cols + jj] = acc;
+    }
+    m_last = m_s[nt];
+    __syncthreads();
+    if (tid == 0) m_s[0] = m_last;
   }
   if (active) {
-    if (DIM > 0) {
 #pragma unroll
-      for (int d = 0; d < (DIM > 0 ? DIM : 1); ++d) st[(size_t)d * cols + jj] = S_r[d];
-    } else {
-      for (int d = 0; d < dim; ++d) st[(size_t)d * cols + jj] = S_s[d * VB + tid];
+    for (int i = 0; i < NPT; ++i) {
+      const int d = ls + DS * i;
+      if (d < dim) st[d] = S[i];
     }
-    st[(size_t)dim * cols + jj] = m;
+    if (ls == 0) st[dim] = m_last;
   }
 }
 
@@ -157,17 +174,20 @@ mlstm_out_kernel(const float* num, const float* m_row, const float* proj, int ld
   }
 }
 
-template <int DIM, typename TB>
-int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const float* proj, int ld,
-                const int32_t* seq_row0, const int32_t* seq_slot, int H, int dim, int vdim, const void* ib,
-                const void* fb, float cap, float q_scale, float* state, float* num, float* m_row) {
+template <int DS, int NPT, typename TB>
+int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int ld, const int32_t* seq_row0,
+                const int32_t* seq_slot, int H, int dim, int vdim, const void* ib, const void* fb, float cap,
+                float q_scale, float* state, float* num, float* m_row) {
+  constexpr int CPB = SCAN_THREADS / DS;
+  const size_t smem = sizeof(float) * ((size_t)2 * tc * DS * NPT + (size_t)tc * CPB + 3 * tc + 1);
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(mlstm_scan_kernel<DIM, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(mlstm_scan_kernel<DS, NPT, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_mlstm_scan: shared memory opt-in failed: %s", cudaGetErrorString(e));
   }
-  sb_launch<SB_K_OTHER>(mlstm_scan_kernel<DIM, TB>, grid, dim3(VB), smem, stream, proj, ld, seq_row0, seq_slot, H, dim,
-                        vdim, (const TB*)ib, (const TB*)fb, cap, q_scale, state, num, m_row);
+  const dim3 grid(n_seqs, H, (vdim + 1 + CPB - 1) / CPB);
+  sb_launch<SB_K_OTHER>(mlstm_scan_kernel<DS, NPT, TB>, grid, dim3(SCAN_THREADS), smem, stream, proj, ld, seq_row0,
+                        seq_slot, H, dim, vdim, tc, (const TB*)ib, (const TB*)fb, cap, q_scale, state, num, m_row);
   return SB_OK;
 }
 
@@ -182,20 +202,22 @@ extern "C" int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_r
     SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: seqs=%d heads=%d dim=%d vdim=%d", n_seqs, n_heads, dim, vdim);
   if (!(cap > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: gate cap %g must be positive", cap);
   if (!sb_valid_dtype(bias_dtype)) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: dtype code %d", bias_dtype);
-  if (n_heads > 65535 || n_seqs > 2147483647 / 1) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: %d heads", n_heads);
+  if (n_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: %d heads", n_heads);
+  if (dim > 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: key size %d is above 1024", dim);
   const int ld = 2 * n_heads * dim + 2 * n_heads * vdim + 2 * n_heads;
-  const dim3 grid(n_seqs, n_heads, (vdim + 1 + VB - 1) / VB);
-  const bool in_regs = dim == 16 || dim == 32 || dim == 64 || dim == 128;
-  const size_t smem = sizeof(float) * ((size_t)2 * TC * dim + TC * VB + 2 * TC + (in_regs ? 0 : (size_t)dim * VB));
-  if (smem > 200 * 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: key size %d needs %zu bytes of shared memory", dim, smem);
+  // tokens staged at a time: as many as keep q and k of a chunk within 32 KB
+  int tc = MAX_TC;
+  while (tc > 4 && (size_t)tc * dim * 8 > 32 * 1024) tc >>= 1;
   int rc = SB_OK;
-#define SB_SCAN(D) rc = launch_scan<D, TB>(grid, smem, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, i_bias, f_bias, cap, q_scale, state, num, m_row)
+#define SB_SCAN(DS, NPT) rc = launch_scan<DS, NPT, TB>(n_seqs, tc, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, i_bias, f_bias, cap, q_scale, state, num, m_row)
   SB_DISPATCH_DTYPE(bias_dtype, TB, {
-    if (dim == 16) SB_SCAN(16);
-    else if (dim == 32) SB_SCAN(32);
-    else if (dim == 64) SB_SCAN(64);
-    else if (dim == 128) SB_SCAN(128);
-    else SB_SCAN(0);
+    if (dim <= 16) SB_SCAN(16, 1);
+    else if (dim <= 32) SB_SCAN(16, 2);
+    else if (dim <= 64) SB_SCAN(16, 4);
+    else if (dim <= 128) SB_SCAN(16, 8);
+    else if (dim <= 256) SB_SCAN(16, 16);
+    else if (dim <= 512) SB_SCAN(32, 16);
+    else SB_SCAN(32, 32);
   });
 #undef SB_SCAN
   if (rc != SB_OK) return rc;

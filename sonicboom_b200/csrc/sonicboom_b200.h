@@ -173,8 +173,8 @@ int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, con
 
 /* ---- matrix-memory recurrence (mLSTM) ----
  * proj[r] = [q heads*dim | k heads*dim | v heads*vdim | g heads*vdim | x_i heads | x_f heads] float32.
- * state: float32 [slot, heads, dim + 1, vdim + 1] (column vdim is the normalizer, row dim the running
- * maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
+ * state: float32 [slot, heads, vdim + 1, dim + 1] (column vdim is the normalizer; after a column's dim
+ * values comes its copy of the running maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
  * state after the last row; num [rows, heads, vdim + 1] and m_row [rows, heads] receive the
  * numerators and maxima.  sb_mlstm_out divides, norms each head (eps), applies norm_w
  * [heads*vdim] and the gate sigmoid(g): out [rows, heads*vdim]. */

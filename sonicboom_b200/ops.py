@@ -674,10 +674,10 @@ def mlstm_scan(proj: torch.Tensor, plan, n_heads: int, dim: int, vdim: int, i_bi
                f_bias: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor,
                num: torch.Tensor, m_row: torch.Tensor) -> torch.Tensor:
     """Walks every sequence's rows of the step through the recurrence, from and to the state
-    rows of the sequences' slots (float32 [slots, heads, dim + 1, vdim + 1])."""
+    rows of the sequences' slots (float32 [slots, heads, vdim + 1, dim + 1])."""
     rows = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.shape[1] == 2 * n_heads * (dim + vdim + 1)
-    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (n_heads, dim + 1, vdim + 1)
+    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (n_heads, vdim + 1, dim + 1)
     assert num.dtype == torch.float32 and tuple(num.shape) == (rows, n_heads, vdim + 1)
     assert m_row.dtype == torch.float32 and tuple(m_row.shape) == (rows, n_heads)
     assert i_bias.dtype == f_bias.dtype and i_bias.numel() == f_bias.numel() == n_heads

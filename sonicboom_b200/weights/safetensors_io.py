@@ -168,4 +168,4 @@ def write_safetensors(path, tensors, metadata=None) -> None:
             if t.dtype != dtype or tuple(t.shape) != tuple(shape):
                 raise SafetensorsError(f"{name}: produced {t.dtype} {tuple(t.shape)}, "
                                        f"announced {dtype} {tuple(shape)}")
-            fh.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            fh.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")
