@@ -552,7 +552,7 @@ def run_zolulix(args) -> int:
 
         class Plan:
             n_seqs = 1 if rows > 64 else rows
-        per = rows // Plan.n_seqs
+        per = Plan.max_new = rows // Plan.n_seqs
         Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
         Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
         rproj = torch.randn(rows, 2 * rh * (rdim + rvd + 1), device=dev) * 0.1

@@ -44,10 +44,10 @@ CORE = {
     "sb_gemm_tc5_force_width": ("v", "i"),
     "sb_norm_add": ("i", "ppiipifppifpis"),
     "sb_depth_mix": ("i", "pzipiiippifpis"),
-    "sb_glu_clamped": ("i", "piiffpis"),
+    "sb_glu_clamped": ("i", "piiffipis"),
     "sb_latent_prep": ("i", "piiiiiipppppipifpipiis"),
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),
-    "sb_mlstm_scan": ("i", "pippiiippiffppps"),
+    "sb_mlstm_scan": ("i", "pippiiippiffippps"),
     "sb_mlstm_out": ("i", "pppiiiipifpis"),
     "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
     "sb_sample_params_size": ("i", ""),

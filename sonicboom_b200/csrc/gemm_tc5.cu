@@ -66,6 +66,14 @@ __device__ __forceinline__ float sb_silu_out(float x) {
   return sb_silu(x);
 }
 
+// What the gated epilogue makes of a gate and its up value: silu(gate) * up, or, with a limit,
+// a sigmoid(slope a) (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit).
+template <typename TO, typename P>
+__device__ __forceinline__ float sb_gated(const P& p, float gate, float up) {
+  if (p.gate_limit > 0.0f) return sb_glu_clamped(gate, up, p.gate_limit, p.gate_slope);
+  return sb_silu_out<TO>(gate) * up;
+}
+
 template <typename TB>
 __device__ __forceinline__ float bias_at(const void* bias, int n) {
   return sb_to_f32<TB>(((const TB*)bias)[n]);
@@ -83,6 +91,7 @@ struct Tc5Params {
   const char* warm;            // asked into L2 by every block as it ends (or null)
   size_t warm_bytes;
   int rowwise;                 // the many-rows epilogue may use 16-byte accesses along a row
+  float gate_limit, gate_slope;   // gated epilogue: limit > 0 selects the clamped form, else silu(gate) * up
 };
 
 constexpr int stage_bytes(int bn) { return (BM + bn) * BK * 2; }
@@ -130,8 +139,8 @@ __device__ __forceinline__ void store_chunk_rowwise(const Tc5Params& p, const ui
     float o[16];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      o[j] = sb_silu_out<TO>(v[j]) * v[j + 8];
-      o[j + 8] = sb_silu_out<TO>(v[j + 16]) * v[j + 24];
+      o[j] = sb_gated<TO>(p, v[j], v[j + 8]);
+      o[j + 8] = sb_gated<TO>(p, v[j + 16], v[j + 24]);
     }
     store_row((TO*)p.out + (size_t)m * (p.N / 2) + n0 / 2, o, 16);
     return;
@@ -192,7 +201,7 @@ __device__ __forceinline__ void store_chunk(const Tc5Params& p, float* stage, co
       const int row = rr + (lane >> 4), m = m_base + row;
       if (m < p.M && live)
         ((TO*)p.out)[(size_t)m * (p.N / 2) + n0 / 2 + o] =
-            sb_from_f32<TO>(sb_silu_out<TO>(stage[row * 33 + src]) * stage[row * 33 + src + 8]);
+            sb_from_f32<TO>(sb_gated<TO>(p, stage[row * 33 + src], stage[row * 33 + src + 8]));
     }
     return;
   }
@@ -385,7 +394,7 @@ gemm_tc5_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int tok = t0 + (gate ? j : j + 1);
             const float g = gate ? a0 : other, up = gate ? other : a1;
             if (live && tok < p.M)
-              ((TO*)p.out)[(size_t)tok * (p.N / 2) + col] = sb_from_f32<TO>(sb_silu_out<TO>(g) * up);
+              ((TO*)p.out)[(size_t)tok * (p.N / 2) + col] = sb_from_f32<TO>(sb_gated<TO>(p, g, up));
           }
         } else {
 #pragma unroll
@@ -587,7 +596,7 @@ tc5_reduce_kernel(const Tc5Params p, int bn) {
     const int o = o0 + i;
     if (o >= n_out) break;
     float v = acc[i];
-    if (p.epilogue == SB_EPI_SWIGLU) v = sb_silu(v) * up[i];
+    if (p.epilogue == SB_EPI_SWIGLU) v = p.gate_limit > 0.0f ? sb_glu_clamped(v, up[i], p.gate_limit, p.gate_slope) : sb_silu(v) * up[i];
     else if (p.epilogue == SB_EPI_BIAS)
       v += p.bias_dtype == SB_F32 ? bias_at<float>(p.bias, o) : bias_at<bf16>(p.bias, o);
     else if (p.epilogue == SB_EPI_RESIDUAL) v += p.residual[(size_t)j * p.N + o];
@@ -1116,6 +1125,8 @@ static int tc5_run(const void* A, int a_dtype, const void* W, int w_dtype, int M
   // (SB_TC5_ROWWISE=0: never, for measurements)
   static const bool rowwise_on = [] { const char* e = getenv("SB_TC5_ROWWISE"); return !(e && e[0] == '0'); }();
   p.rowwise = rowwise_on && N % 16 == 0 && (((uintptr_t)out | (uintptr_t)residual | (uintptr_t)bias) & 15) == 0;
+  p.gate_limit = extras && epilogue == SB_EPI_SWIGLU ? extras->gate_limit : 0.0f;
+  p.gate_slope = extras ? extras->gate_slope : 1.0f;
   p.warm = extras ? (const char*)extras->warm : nullptr;
   p.warm_bytes = extras ? sb_warm_bytes(extras->warm, extras->warm_bytes) : 0;
   CUtensorMap ma, mb;

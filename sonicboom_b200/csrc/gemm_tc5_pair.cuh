@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(256) tc5_splitk_reduce_kernel(const Tc5Params 
   if (p.epilogue == SB_EPI_SWIGLU) {
     float o[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = sb_silu_out<TO>(v[j]) * v[j + 8];
+    for (int j = 0; j < 8; ++j) o[j] = sb_gated<TO>(p, v[j], v[j + 8]);
     store_row((TO*)p.out + (size_t)m * (p.N / 2) + n0 / 2, o, 8);
     return;
   }

@@ -146,6 +146,35 @@ head_linear_kernel(const TI* in, size_t in_ld, size_t in_hs, const TW* __restric
   }
 }
 
+// The same for at most HS_ROWS rows (decode): a warp per output column of a head streams that
+// column's weights once, the lanes share out K, and the rows' sums meet by shuffles.
+constexpr int HS_ROWS = 8, HS_WARPS = 8;
+
+template <typename TI, typename TW, typename TO>
+__global__ void __launch_bounds__(HS_WARPS * 32)
+head_linear_skinny_kernel(const TI* in, size_t in_ld, size_t in_hs, const TW* __restrict__ W, int n_rows,
+                          int N, int K, TO* out, size_t out_ld, size_t out_hs) {
+  sb_pdl_launch();
+  const int h = blockIdx.y, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * HS_WARPS + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const TW* w = W + ((size_t)h * N + n) * K;
+  const TI* a = in + (size_t)h * in_hs;
+  float acc[HS_ROWS] = {};
+  sb_pdl_wait();
+  for (int k = lane; k < K; k += 32) {
+    const float wv = sb_to_f32<TW>(w[k]);
+#pragma unroll
+    for (int r = 0; r < HS_ROWS; ++r)
+      if (r < n_rows) acc[r] = fmaf(wv, sb_to_f32<TI>(a[(size_t)r * in_ld + k]), acc[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < HS_ROWS; ++r) {
+    const float v = sb_warp_sum(acc[r]);
+    if (lane == 0 && r < n_rows) out[(size_t)r * out_ld + (size_t)h * out_hs + n] = sb_from_f32<TO>(v);
+  }
+}
+
 }  // namespace
 
 extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int dim, int rd, int rank,
@@ -186,11 +215,16 @@ extern "C" int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t
   if (!sb_valid_dtype(in_dtype) || !sb_valid_dtype(w_dtype) || !sb_valid_dtype(out_dtype))
     SB_FAIL(SB_ERR_ARG, "sb_head_linear: dtype codes %d %d %d", in_dtype, w_dtype, out_dtype);
   const dim3 grid((n_rows + HL_BM - 1) / HL_BM, (N + HL_BN - 1) / HL_BN, n_heads);
+  const dim3 skinny((N + HS_WARPS - 1) / HS_WARPS, n_heads);
   SB_DISPATCH_DTYPE(in_dtype, TI, {
     SB_DISPATCH_DTYPE(w_dtype, TW, {
       SB_DISPATCH_DTYPE(out_dtype, TO, {
-        sb_launch<SB_K_OTHER>(head_linear_kernel<TI, TW, TO>, grid, dim3(HL_THREADS), 0, stream, (const TI*)in, in_ld,
-                              in_hs, (const TW*)W, n_rows, N, K, (TO*)out, out_ld, out_hs);
+        if (n_rows <= HS_ROWS)
+          sb_launch<SB_K_OTHER>(head_linear_skinny_kernel<TI, TW, TO>, skinny, dim3(HS_WARPS * 32), 0, stream,
+                                (const TI*)in, in_ld, in_hs, (const TW*)W, n_rows, N, K, (TO*)out, out_ld, out_hs);
+        else
+          sb_launch<SB_K_OTHER>(head_linear_kernel<TI, TW, TO>, grid, dim3(HL_THREADS), 0, stream, (const TI*)in, in_ld,
+                                in_hs, (const TW*)W, n_rows, N, K, (TO*)out, out_ld, out_hs);
       });
     });
   });

@@ -1,6 +1,6 @@
 // The matrix-memory recurrence (mLSTM) with exponential gates and a running maximum.
 //
-// Per sequence and head, with q (already scaled), k in R^dim, v in R^vdim and the log gates
+// Per sequence and head, with q (scaled), k in R^dim, v in R^vdim and the log gates
 // i_t (input) and f_t (forget):
 //     m_t = max(f_t + m_{t-1}, i_t)
 //     S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T          S in R^{dim x vdim}
@@ -40,7 +40,17 @@ __device__ __forceinline__ float log_sigmoid(float z) {
   return z >= 0.0f ? -log1pf(expf(-z)) : z - log1pf(expf(z));
 }
 
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
 // DS lanes share a column, NPT values of it each (DS * NPT >= dim; values past dim stay zero).
+// A chunk's q, k, v and gate pre-activations are copied into one of two shared-memory stages
+// with cp.async while the chunk before it is walked.
 template <int DS, int NPT, typename TB>
 __global__ void __launch_bounds__(SCAN_THREADS)
 mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int32_t* seq_slot, int H,
@@ -49,10 +59,8 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
   constexpr int CPB = SCAN_THREADS / DS;   // columns per block
   extern __shared__ float smem[];
   const int dim_p = DS * NPT;
-  float* q_s = smem;                       // [tc][dim_p]
-  float* k_s = q_s + tc * dim_p;           // [tc][dim_p]
-  float* v_s = k_s + tc * dim_p;           // [tc][CPB]
-  float* ig_s = v_s + tc * CPB;            // [tc] log input gate, then its factor exp(i - m)
+  const int stage = 2 * tc * dim_p + tc * CPB + 2 * tc;      // floats of one stage: q, k, v, x_i, x_f
+  float* ig_s = smem + 2 * stage;          // [tc] log input gate, then its factor exp(i - m)
   float* fg_s = ig_s + tc;                 // [tc] log forget gate, then its factor exp(f + m' - m)
   float* m_s = fg_s + tc;                  // [tc + 1]: m before the chunk, then after each token
   sb_pdl_launch();
@@ -63,7 +71,47 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
   const int row0 = seq_row0[b], T = seq_row0[b + 1] - row0;
   float* st = state + (((size_t)seq_slot[b] * H + h) * cols + (active ? jj : 0)) * (size_t)(dim + 1);
   const float bi = sb_to_f32<TB>(i_bias[h]), bf = sb_to_f32<TB>(f_bias[h]);
+  const int q_off = h * dim, k_off = H * dim + h * dim, v_off = 2 * H * dim + h * vdim;
+  const int i_off = 2 * H * dim + 2 * H * vdim + h, f_off = i_off + H;
+  // what cp.async never writes: the padding past dim, and the columns past vdim (1 for the
+  // normalizer's column, 0 beyond)
+  for (int e = tid; e < 2 * stage; e += SCAN_THREADS) {
+    const int r = e % stage;
+    float v = 0.0f;
+    if (r >= 2 * tc * dim_p && r < 2 * tc * dim_p + tc * CPB)
+      v = blockIdx.z * CPB + (r - 2 * tc * dim_p) % CPB == vdim ? 1.0f : 0.0f;
+    smem[e] = v;
+  }
+  __syncthreads();
   sb_pdl_wait();
+
+  auto load_chunk = [&](int t0, int buf) {
+    const int nt = min(tc, T - t0);
+    float* q_s = smem + buf * stage;
+    float* k_s = q_s + tc * dim_p;
+    float* v_s = k_s + tc * dim_p;
+    float* xi_s = v_s + tc * CPB;
+    float* xf_s = xi_s + tc;
+    for (int e = tid; e < nt * dim; e += SCAN_THREADS) {
+      const int tt = e / dim, d = e % dim;
+      const float* src = proj + (size_t)(row0 + t0 + tt) * ld;
+      cp_async4(q_s + tt * dim_p + d, src + q_off + d);
+      cp_async4(k_s + tt * dim_p + d, src + k_off + d);
+    }
+    const int nv = min(CPB, vdim - (int)blockIdx.z * CPB);      // columns of this block that are values
+    for (int e = tid; e < nt * nv; e += SCAN_THREADS) {
+      const int tt = e / nv, j = e % nv;
+      cp_async4(v_s + tt * CPB + j, proj + (size_t)(row0 + t0 + tt) * ld + v_off + blockIdx.z * CPB + j);
+    }
+    if (tid < nt) {
+      const float* src = proj + (size_t)(row0 + t0 + tid) * ld;
+      cp_async4(xi_s + tid, src + i_off);
+      cp_async4(xf_s + tid, src + f_off);
+    }
+    cp_async_commit();
+  };
+
+  load_chunk(0, 0);
   float S[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; ++i) {
@@ -71,25 +119,25 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
     S[i] = (active && d < dim) ? st[d] : 0.0f;
   }
   if (tid == 0) m_s[0] = st[dim];
-  const int q_off = h * dim, k_off = H * dim + h * dim, v_off = 2 * H * dim + h * vdim;
-  const int i_off = 2 * H * dim + 2 * H * vdim + h, f_off = i_off + H;
   float m_last = 0.0f;
-  for (int t0 = 0; t0 < T; t0 += tc) {
+  int buf = 0;
+  for (int t0 = 0; t0 < T; t0 += tc, buf ^= 1) {
     const int nt = min(tc, T - t0);
-    for (int e = tid; e < nt * dim_p; e += SCAN_THREADS) {
-      const int tt = e / dim_p, d = e % dim_p;
-      const float* src = proj + (size_t)(row0 + t0 + tt) * ld;
-      q_s[e] = d < dim ? src[q_off + d] * q_scale : 0.0f;
-      k_s[e] = d < dim ? src[k_off + d] : 0.0f;
+    if (t0 + tc < T) {
+      load_chunk(t0 + tc, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
     }
-    for (int e = tid; e < nt * CPB; e += SCAN_THREADS) {
-      const int tt = e / CPB, j = blockIdx.z * CPB + e % CPB;
-      v_s[e] = j < vdim ? proj[(size_t)(row0 + t0 + tt) * ld + v_off + j] : (j == vdim ? 1.0f : 0.0f);
-    }
+    __syncthreads();
+    const float* q_s = smem + buf * stage;
+    const float* k_s = q_s + tc * dim_p;
+    const float* v_s = k_s + tc * dim_p;
+    const float* xi_s = v_s + tc * CPB;
+    const float* xf_s = xi_s + tc;
     if (tid < nt) {
-      const float* src = proj + (size_t)(row0 + t0 + tid) * ld;
-      ig_s[tid] = cap * tanhf((src[i_off] + bi) / cap);
-      fg_s[tid] = log_sigmoid(cap * tanhf((src[f_off] + bf) / cap));
+      ig_s[tid] = cap * tanhf((xi_s[tid] + bi) / cap);
+      fg_s[tid] = log_sigmoid(cap * tanhf((xf_s[tid] + bf) / cap));
     }
     __syncthreads();
     if (tid == 0) {
@@ -108,25 +156,44 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
       if (blockIdx.z == 0) m_row[(size_t)(row0 + t0 + tid) * H + h] = mn;
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float a = fg_s[tt], bv = ig_s[tt] * v_s[tt * CPB + c];
-      const float* kt = k_s + tt * dim_p + ls;
-      const float* qt = q_s + tt * dim_p + ls;
-      float acc0 = 0.0f, acc1 = 0.0f;
+    // DS tokens at a time: every lane keeps its partial sum of each of them, and the DS x DS
+    // partial sums are added up across the lanes in log2(DS) exchanges of halves (DS - 1 shuffles
+    // for DS tokens), after which lane ls holds the whole sum of token ls of the group.
+    for (int g0 = 0; g0 < nt; g0 += DS) {
+      float acc[DS];
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const float sv = fmaf(S[i], a, kt[DS * i] * bv);
-        S[i] = sv;
-        if (i & 1) acc1 = fmaf(sv, qt[DS * i], acc1);
-        else acc0 = fmaf(sv, qt[DS * i], acc0);
+      for (int u = 0; u < DS; ++u) {
+        const int tt = g0 + u;
+        acc[u] = 0.0f;
+        if (tt < nt) {
+          const float a = fg_s[tt], bv = ig_s[tt] * v_s[tt * CPB + c];
+          const float* kt = k_s + tt * dim_p + ls;
+          const float* qt = q_s + tt * dim_p + ls;
+          float acc1 = 0.0f;
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) {
+            const float sv = fmaf(S[i], a, kt[DS * i] * bv);
+            S[i] = sv;
+            if (i & 1) acc1 = fmaf(sv, qt[DS * i], acc1);
+            else acc[u] = fmaf(sv, qt[DS * i], acc[u]);
+          }
+          acc[u] += acc1;
+        }
       }
-      float acc = acc0 + acc1;
 #pragma unroll
-      for (int o = DS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (active && ls == 0) num[((size_t)(row0 + t0 + tt) * H + h) * cols + jj] = acc;
+      for (int o = DS / 2; o > 0; o >>= 1) {
+        const bool up = (ls & o) != 0;
+#pragma unroll
+        for (int u = 0; u < o; ++u) {
+          const float give = up ? acc[u] : acc[u + o];
+          const float keep = up ? acc[u + o] : acc[u];
+          acc[u] = keep + __shfl_xor_sync(0xffffffffu, give, o);
+        }
+      }
+      if (active && g0 + ls < nt) num[((size_t)(row0 + t0 + g0 + ls) * H + h) * cols + jj] = acc[0] * q_scale;
     }
     m_last = m_s[nt];
-    __syncthreads();
+    __syncthreads();                       // everyone is done with this stage and with m_s
     if (tid == 0) m_s[0] = m_last;
   }
   if (active) {
@@ -179,7 +246,7 @@ int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int 
                 const int32_t* seq_slot, int H, int dim, int vdim, const void* ib, const void* fb, float cap,
                 float q_scale, float* state, float* num, float* m_row) {
   constexpr int CPB = SCAN_THREADS / DS;
-  const size_t smem = sizeof(float) * ((size_t)2 * tc * DS * NPT + (size_t)tc * CPB + 3 * tc + 1);
+  const size_t smem = sizeof(float) * (2 * ((size_t)2 * tc * DS * NPT + (size_t)tc * CPB + 2 * tc) + 3 * tc + 1);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(mlstm_scan_kernel<DS, NPT, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
@@ -195,19 +262,21 @@ int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int 
 
 extern "C" int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_row0,
                              const int32_t* seq_slot, int n_heads, int dim, int vdim, const void* i_bias,
-                             const void* f_bias, int bias_dtype, float cap, float q_scale, float* state,
-                             float* num, float* m_row, cudaStream_t stream) {
+                             const void* f_bias, int bias_dtype, float cap, float q_scale, int max_new,
+                             float* state, float* num, float* m_row, cudaStream_t stream) {
   if (n_seqs <= 0 || n_heads <= 0 || dim <= 0 || vdim <= 0 || !proj || !seq_row0 || !seq_slot || !state || !num ||
       !m_row || !i_bias || !f_bias)
     SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: seqs=%d heads=%d dim=%d vdim=%d", n_seqs, n_heads, dim, vdim);
   if (!(cap > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: gate cap %g must be positive", cap);
   if (!sb_valid_dtype(bias_dtype)) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: dtype code %d", bias_dtype);
   if (n_heads > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: %d heads", n_heads);
+  if (max_new < 1) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: max_new = %d", max_new);
   if (dim > 1024) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_mlstm_scan: key size %d is above 1024", dim);
   const int ld = 2 * n_heads * dim + 2 * n_heads * vdim + 2 * n_heads;
   // tokens staged at a time: as many as keep q and k of a chunk within 32 KB
   int tc = MAX_TC;
   while (tc > 4 && (size_t)tc * dim * 8 > 32 * 1024) tc >>= 1;
+  while (tc > 1 && tc / 2 >= max_new) tc >>= 1;            // no longer than the step's longest portion
   int rc = SB_OK;
 #define SB_SCAN(DS, NPT) rc = launch_scan<DS, NPT, TB>(n_seqs, tc, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, i_bias, f_bias, cap, q_scale, state, num, m_row)
   SB_DISPATCH_DTYPE(bias_dtype, TB, {

@@ -73,6 +73,8 @@ typedef struct SbLinearExtras {
   const void* warm;            /* null: nothing; else bytes a later kernel will stream */
   size_t warm_bytes;
   const SbRopeStore* rope;     /* null: none; only where sb_gemm_tc5_fuses_rope says so */
+  float gate_limit;            /* SB_EPI_SWIGLU only: > 0 makes the gated epilogue a sigmoid(gate_slope a) (b + 1), */
+  float gate_slope;            /* a = min(gate, limit), b = clamp(up, -limit, limit); 0: silu(gate) * up */
 } SbLinearExtras;
 
 /* One row's sampling record (sb_sample reads an array of them from device memory). */
@@ -150,10 +152,11 @@ int sb_norm_add(const float* y, const float* x, int n_rows, int width, const voi
 int sb_depth_mix(const float* planes, size_t plane, int n_inputs, const void* coef, int coef_dtype,
                  int n_rows, int width, float* out, const void* next_w, int next_w_dtype,
                  float next_eps, void* normed, int normed_dtype, sb_stream_t stream);
-/* gu[r] = [gate (ff) | up (ff)]; out[r, c] = a sigmoid(alpha a) (b + 1), a = min(gate, limit),
+/* gu[r] = [gate (ff) | up (ff)], or with `interleaved` blocks of 8 gates followed by the 8 up values of
+ * the same outputs (ff a multiple of 8); out[r, c] = a sigmoid(alpha a) (b + 1), a = min(gate, limit),
  * b = clamp(up, -limit, limit). */
-int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, void* out,
-                   int out_dtype, sb_stream_t stream);
+int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, int interleaved,
+                   void* out, int out_dtype, sb_stream_t stream);
 
 /* ---- attention over a cached latent ----
  * proj[r] = [n_heads x (dim | rd) | rank | rd] (the last two only with has_kv).  Rotates the first
@@ -176,11 +179,12 @@ int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, con
  * state: float32 [slot, heads, vdim + 1, dim + 1] (column vdim is the normalizer; after a column's dim
  * values comes its copy of the running maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
  * state after the last row; num [rows, heads, vdim + 1] and m_row [rows, heads] receive the
- * numerators and maxima.  sb_mlstm_out divides, norms each head (eps), applies norm_w
+ * numerators and maxima; max_new is an upper bound of any sequence's rows in the step.  sb_mlstm_out divides, norms each head (eps), applies norm_w
  * [heads*vdim] and the gate sigmoid(g): out [rows, heads*vdim]. */
 int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_row0, const int32_t* seq_slot,
                   int n_heads, int dim, int vdim, const void* i_bias, const void* f_bias, int bias_dtype,
-                  float cap, float q_scale, float* state, float* num, float* m_row, sb_stream_t stream);
+                  float cap, float q_scale, int max_new, float* state, float* num, float* m_row,
+                  sb_stream_t stream);
 int sb_mlstm_out(const float* num, const float* m_row, const float* proj, int n_rows, int n_heads,
                  int dim, int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out,
                  int out_dtype, sb_stream_t stream);

@@ -12,9 +12,32 @@
 
 namespace {
 
-constexpr int ROW_THREADS = 256;
+// A row is walked in groups of V values (V = 4: 16-byte accesses, for widths that are multiples
+// of 4 and aligned rows) by NT threads: 256 when the launch has rows enough to fill the GPU, 1024
+// when it has few (decode), so that a row's loads are in flight together.
+template <int V>
+struct Vec {
+  float v[V];
+};
+template <int V>
+__device__ __forceinline__ Vec<V> ld(const float* p) {
+  Vec<V> r;
+  if (V == 4) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    r.v[0] = f.x; r.v[1 % V] = f.y; r.v[2 % V] = f.z; r.v[3 % V] = f.w;
+  } else {
+    r.v[0] = *p;
+  }
+  return r;
+}
+template <int V>
+__device__ __forceinline__ void st(float* p, const Vec<V>& r) {
+  if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1 % V], r.v[2 % V], r.v[3 % V]);
+  else *p = r.v[0];
+}
 
-// Sum over the block, the same value in every thread.  `red` holds ROW_THREADS / 32 + 1 floats.
+// Sum over the block, the same value in every thread.  `red` holds NT / 32 + 1 floats.
+template <int NT>
 __device__ __forceinline__ float block_sum(float s, float* red) {
   s = sb_warp_sum(s);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -23,28 +46,31 @@ __device__ __forceinline__ float block_sum(float s, float* red) {
   __syncthreads();
   if (threadIdx.x == 0) {
     float total = 0.0f;
-    for (int i = 0; i < ROW_THREADS / 32; ++i) total += red[i];
-    red[ROW_THREADS / 32] = total;
+    for (int i = 0; i < NT / 32; ++i) total += red[i];
+    red[NT / 32] = total;
   }
   __syncthreads();
-  return red[ROW_THREADS / 32];
+  return red[NT / 32];
 }
 
 // Writes normed[i] = out[i] * inv * next_w[i] for the thread's own elements of the row it wrote.
-template <typename TN, typename TO>
+template <int NT, int V, typename TN, typename TO>
 __device__ __forceinline__ void write_normed(const float* o, int width, float sq, float next_eps,
                                              const TN* __restrict__ next_w, TO* nrm, float* red) {
-  const float total = block_sum(sq, red);
+  const float total = block_sum<NT>(sq, red);
   const float inv = 1.0f / sqrtf(total / (float)width + next_eps);
-  for (int i = threadIdx.x; i < width; i += ROW_THREADS)
-    nrm[i] = sb_from_f32<TO>((o[i] * inv) * sb_to_f32<TN>(next_w[i]));
+  for (int i = threadIdx.x * V; i < width; i += NT * V) {
+    const Vec<V> x = ld<V>(o + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) nrm[i + j] = sb_from_f32<TO>((x.v[j] * inv) * sb_to_f32<TN>(next_w[i + j]));
+  }
 }
 
-template <typename TW, typename TN, typename TO>
-__global__ void __launch_bounds__(ROW_THREADS)
+template <int NT, int V, typename TW, typename TN, typename TO>
+__global__ void __launch_bounds__(NT)
 norm_add_kernel(const float* y, const float* x, int width, const TW* __restrict__ w, float eps,
                 float* out, const TN* __restrict__ next_w, float next_eps, TO* normed) {
-  __shared__ float red[ROW_THREADS / 32 + 1];
+  __shared__ float red[NT / 32 + 1];
   sb_pdl_launch();
   sb_pdl_wait();
   const size_t r = blockIdx.x;
@@ -52,54 +78,73 @@ norm_add_kernel(const float* y, const float* x, int width, const TW* __restrict_
   const float* xr = x + r * width;
   float* o = out + r * width;
   float s = 0.0f;
-  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
-    const float v = yr[i];
-    s = fmaf(v, v, s);
+  for (int i = threadIdx.x * V; i < width; i += NT * V) {
+    const Vec<V> a = ld<V>(yr + i);
+#pragma unroll
+    for (int j = 0; j < V; ++j) s = fmaf(a.v[j], a.v[j], s);
   }
-  const float inv = 1.0f / sqrtf(block_sum(s, red) / (float)width + eps);
+  const float inv = 1.0f / sqrtf(block_sum<NT>(s, red) / (float)width + eps);
   float sq = 0.0f;
-  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
-    const float v = xr[i] + (yr[i] * inv) * sb_to_f32<TW>(w[i]);
-    o[i] = v;
-    sq = fmaf(v, v, sq);
+  for (int i = threadIdx.x * V; i < width; i += NT * V) {
+    const Vec<V> a = ld<V>(yr + i), b = ld<V>(xr + i);
+    Vec<V> v;
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      v.v[j] = b.v[j] + (a.v[j] * inv) * sb_to_f32<TW>(w[i + j]);
+      sq = fmaf(v.v[j], v.v[j], sq);
+    }
+    st<V>(o + i, v);
   }
-  if (normed) write_normed<TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
+  if (normed) write_normed<NT, V, TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
 }
 
 constexpr int MIX_MAX = 256;       // most planes one depth mix adds up
 
-template <typename TC, typename TN, typename TO>
-__global__ void __launch_bounds__(ROW_THREADS)
+template <int NT, int V, typename TC, typename TN, typename TO>
+__global__ void __launch_bounds__(NT)
 depth_mix_kernel(const float* planes, size_t plane, int n_inputs, const TC* __restrict__ coef,
                  int width, float* out, const TN* __restrict__ next_w, float next_eps, TO* normed) {
-  __shared__ float red[ROW_THREADS / 32 + 1];
+  __shared__ float red[NT / 32 + 1];
   __shared__ float c[MIX_MAX];
   sb_pdl_launch();
-  for (int j = threadIdx.x; j < n_inputs; j += ROW_THREADS) c[j] = sb_to_f32<TC>(coef[j]);
+  for (int j = threadIdx.x; j < n_inputs; j += NT) c[j] = sb_to_f32<TC>(coef[j]);
   __syncthreads();
   sb_pdl_wait();
   const size_t r = blockIdx.x;
   float* o = out + r * width;
   float sq = 0.0f;
-  for (int i = threadIdx.x; i < width; i += ROW_THREADS) {
+  for (int i = threadIdx.x * V; i < width; i += NT * V) {
     const float* p = planes + r * width + i;
-    float v = 0.0f;
-    for (int j = 0; j < n_inputs; ++j) v = fmaf(c[j], p[(size_t)j * plane], v);
-    o[i] = v;
-    sq = fmaf(v, v, sq);
+    Vec<V> v;
+#pragma unroll
+    for (int j = 0; j < V; ++j) v.v[j] = 0.0f;
+#pragma unroll 4
+    for (int k = 0; k < n_inputs; ++k) {
+      const Vec<V> a = ld<V>(p + (size_t)k * plane);
+#pragma unroll
+      for (int j = 0; j < V; ++j) v.v[j] = fmaf(c[k], a.v[j], v.v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < V; ++j) sq = fmaf(v.v[j], v.v[j], sq);
+    st<V>(o + i, v);
   }
-  if (normed) write_normed<TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
+  if (normed) write_normed<NT, V, TN, TO>(o, width, sq, next_eps, next_w, normed + r * width, red);
 }
 
 // y = a * sigmoid(alpha a) * (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit);
 // the input row is [gate (ff) | up (ff)] in float32.
+// With `interleaved` the row is blocks of SB_SWIGLU_BLOCK gates followed by the up values of the same
+// outputs, as the products with a gated epilogue want their weights.
 template <typename TO>
-__global__ void glu_clamped_kernel(const float* gu, size_t n, int ff, float limit, float alpha, TO* out) {
+__global__ void glu_clamped_kernel(const float* gu, size_t n, int ff, float limit, float alpha,
+                                   int interleaved, TO* out) {
   sb_pdl_launch();
   sb_pdl_wait();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
     const size_t r = e / ff, c = e % ff;
-    out[e] = sb_from_f32<TO>(sb_glu_clamped(gu[r * 2 * ff + c], gu[r * 2 * ff + ff + c], limit, alpha));
+    const size_t g = interleaved ? (c / SB_SWIGLU_BLOCK) * 2 * SB_SWIGLU_BLOCK + c % SB_SWIGLU_BLOCK : c;
+    const size_t u = interleaved ? g + SB_SWIGLU_BLOCK : ff + c;
+    out[e] = sb_from_f32<TO>(sb_glu_clamped(gu[r * 2 * ff + g], gu[r * 2 * ff + u], limit, alpha));
   }
 }
 
@@ -116,6 +161,18 @@ __global__ void glu_clamped_kernel(const float* gu, size_t n, int ff, float limi
     }                                          \
   } while (0)
 
+// Launches KERNEL<NT, V, T1, TN, TO> over n_rows blocks: 16-byte accesses when `vec`, 1024 threads
+// a row when the launch has few rows of a wide stream.
+#define SB_ROW_LAUNCH(KERNEL, T1, ...)                                                                        \
+  do {                                                                                                        \
+    if (vec && wide)                                                                                          \
+      sb_launch<SB_K_ELEMENTWISE>(KERNEL<1024, 4, T1, TN, TO>, dim3(n_rows), dim3(1024), 0, stream, __VA_ARGS__); \
+    else if (vec)                                                                                             \
+      sb_launch<SB_K_ELEMENTWISE>(KERNEL<256, 4, T1, TN, TO>, dim3(n_rows), dim3(256), 0, stream, __VA_ARGS__);   \
+    else                                                                                                      \
+      sb_launch<SB_K_ELEMENTWISE>(KERNEL<256, 1, T1, TN, TO>, dim3(n_rows), dim3(256), 0, stream, __VA_ARGS__);   \
+  } while (0)
+
 extern "C" int sb_norm_add(const float* y, const float* x, int n_rows, int width, const void* w,
                            int w_dtype, float eps, float* out, const void* next_w, int next_w_dtype,
                            float next_eps, void* normed, int normed_dtype, cudaStream_t stream) {
@@ -124,11 +181,12 @@ extern "C" int sb_norm_add(const float* y, const float* x, int n_rows, int width
   if (!sb_valid_dtype(w_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_norm_add: dtype codes %d %d %d", w_dtype, next_w_dtype, normed_dtype);
   if (!(eps >= 0.0f) || (normed && !(next_eps >= 0.0f))) SB_FAIL(SB_ERR_ARG, "sb_norm_add: eps %g %g", eps, next_eps);
+  const bool vec = width % 4 == 0 && (((uintptr_t)y | (uintptr_t)x | (uintptr_t)out) & 15) == 0;
+  const bool wide = n_rows <= 256 && width >= 2048;
   SB_DISPATCH_DTYPE(w_dtype, TW, {
     SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
       SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
-        sb_launch<SB_K_ELEMENTWISE>(norm_add_kernel<TW, TN, TO>, dim3(n_rows), dim3(ROW_THREADS), 0, stream, y, x,
-                                    width, (const TW*)w, eps, out, (const TN*)next_w, next_eps, (TO*)normed);
+        SB_ROW_LAUNCH(norm_add_kernel, TW, y, x, width, (const TW*)w, eps, out, (const TN*)next_w, next_eps, (TO*)normed);
       });
     });
   });
@@ -145,14 +203,15 @@ extern "C" int sb_depth_mix(const float* planes, size_t plane, int n_inputs, con
   if (n_inputs < 1 || n_inputs > MIX_MAX)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_depth_mix: %d inputs (1 to %d)", n_inputs, MIX_MAX);
   if (plane < (size_t)n_rows * width) SB_FAIL(SB_ERR_ARG, "sb_depth_mix: planes overlap");
+  const bool vec = width % 4 == 0 && plane % 4 == 0 && (((uintptr_t)planes | (uintptr_t)out) & 15) == 0;
+  const bool wide = n_rows <= 256 && width >= 2048;
   if (!sb_valid_dtype(coef_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_depth_mix: dtype codes %d %d %d", coef_dtype, next_w_dtype, normed_dtype);
   SB_DISPATCH_DTYPE(coef_dtype, TC, {
     SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
       SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
-        sb_launch<SB_K_ELEMENTWISE>(depth_mix_kernel<TC, TN, TO>, dim3(n_rows), dim3(ROW_THREADS), 0, stream, planes,
-                                    plane, n_inputs, (const TC*)coef, width, out, (const TN*)next_w, next_eps,
-                                    (TO*)normed);
+        SB_ROW_LAUNCH(depth_mix_kernel, TC, planes, plane, n_inputs, (const TC*)coef, width, out, (const TN*)next_w,
+                      next_eps, (TO*)normed);
       });
     });
   });
@@ -160,8 +219,10 @@ extern "C" int sb_depth_mix(const float* planes, size_t plane, int n_inputs, con
   return SB_OK;
 }
 
-extern "C" int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, void* out,
-                              int out_dtype, cudaStream_t stream) {
+extern "C" int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha, int interleaved,
+                              void* out, int out_dtype, cudaStream_t stream) {
+  if (interleaved && ff % SB_SWIGLU_BLOCK)
+    SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: %d outputs are no multiple of %d", ff, SB_SWIGLU_BLOCK);
   if (n_rows <= 0 || ff <= 0 || !gu || !out) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: rows=%d ff=%d", n_rows, ff);
   if (!sb_valid_dtype(out_dtype)) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: dtype code %d", out_dtype);
   if (!(limit > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_glu_clamped: limit %g must be positive", limit);
@@ -169,7 +230,7 @@ extern "C" int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, 
   const int blocks = (int)((n + 255) / 256 < 8192 ? (n + 255) / 256 : 8192);
   SB_DISPATCH_DTYPE(out_dtype, TO, {
     sb_launch<SB_K_ELEMENTWISE>(glu_clamped_kernel<TO>, dim3(blocks), dim3(256), 0, stream, gu, n, ff, limit, alpha,
-                                (TO*)out);
+                                interleaved, (TO*)out);
   });
   SB_CHECK_LAUNCH("sb_glu_clamped");
   return SB_OK;

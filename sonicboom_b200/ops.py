@@ -167,8 +167,12 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_NONE,
            bias: torch.Tensor | None = None, residual: torch.Tensor | None = None,
            kernel: str = "auto", norm: tuple | None = None,
-           warm: torch.Tensor | None = None) -> torch.Tensor:
+           warm: torch.Tensor | None = None, gate: tuple | None = None) -> torch.Tensor:
     """out = a @ w.T with a fused epilogue; a [M,K], w [N,K]; float32 accumulation.
+
+    `gate` = (limit, slope) with EPI_SWIGLU makes the gated epilogue the clamped form
+    a * sigmoid(slope a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit): inside the
+    tcgen05 kernel where that runs, else as the plain product followed by `glu_clamped`.
 
     `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
     (out must be float32): in the kernel that finishes the product where one does (the split-K
@@ -193,6 +197,15 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         a = cast(a, torch.float32)
         if w.dtype != torch.float32:
             raise KernelError("linear: a float32 activation needs float32 weights")
+    if gate is not None:
+        assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0
+        fused = a.dtype == torch.bfloat16 and kernel in ("auto", "tc5") and K % 8 == 0 and \
+            (kernel == "tc5" or _pick_kernel(M, N, K, a.device) == "tc5")
+        if not fused:
+            gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
+            linear(a, w, gu, EPI_NONE, kernel=kernel)
+            return glu_clamped(gu, gate[0], gate[1], out, interleaved=True)
+        kernel = "tc5"
     args = (_ptr(a), _code(a.dtype), _ptr(w), _code(w.dtype), M, N, K, epilogue, _ptr(bias),
             _code(bias.dtype) if bias is not None else 0, _ptr(residual), _ptr(out),
             _code(out.dtype), _stream())
@@ -220,8 +233,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
         form = 1 if kernel == "tc5_normal" else 0
         ws = _tc5_workspace(M, N, K, a.device) if form == 0 else None
         extras = None
-        if norm is not None or (warm is not None and WARM):
+        if norm is not None or (warm is not None and WARM) or gate is not None:
             extras = LinearExtras()
+            if gate is not None:
+                extras.gate_limit, extras.gate_slope = float(gate[0]), float(gate[1])
             if norm is not None:
                 extras.norm_weight, extras.norm_weight_dtype = norm_w.data_ptr(), _code(norm_w.dtype)
                 extras.norm_eps, extras.norm_out = norm_eps, norm_out.data_ptr()
@@ -257,7 +272,8 @@ class LinearExtras(ctypes.Structure):
     _fields_ = [("norm_weight", ctypes.c_void_p), ("norm_weight_dtype", ctypes.c_int),
                 ("norm_eps", ctypes.c_float), ("norm_out", ctypes.c_void_p),
                 ("norm_out_dtype", ctypes.c_int), ("warm", ctypes.c_void_p),
-                ("warm_bytes", ctypes.c_size_t), ("rope", ctypes.POINTER(RopeStore))]
+                ("warm_bytes", ctypes.c_size_t), ("rope", ctypes.POINTER(RopeStore)),
+                ("gate_limit", ctypes.c_float), ("gate_slope", ctypes.c_float)]
 
 
 def qkv_rope_store(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, n_q_heads: int,
@@ -617,13 +633,15 @@ def depth_mix(planes: torch.Tensor, n_inputs: int, coef: torch.Tensor, out: torc
     return out
 
 
-def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float, out: torch.Tensor) -> torch.Tensor:
+def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float, out: torch.Tensor,
+                interleaved: bool = False) -> torch.Tensor:
     """out = a * sigmoid(slope a) * (b + 1) with a = min(gate, limit), b = clamp(up, -limit, limit);
-    gate_up is float32 [rows, 2 ff] = [gate | up]."""
+    gate_up is float32 [rows, 2 ff] = [gate | up], or with `interleaved` blocks of SWIGLU_BLOCK
+    gates followed by the up values of the same outputs."""
     rows, ff = out.shape
     assert gate_up.dtype == torch.float32 and tuple(gate_up.shape) == (rows, 2 * ff)
     _check(lib().sb_glu_clamped(_ptr(gate_up), rows, ff, ctypes.c_float(limit), ctypes.c_float(slope),
-                                _ptr(out), _code(out.dtype), _stream()), "glu_clamped")
+                                1 if interleaved else 0, _ptr(out), _code(out.dtype), _stream()), "glu_clamped")
     return out
 
 
@@ -684,7 +702,8 @@ def mlstm_scan(proj: torch.Tensor, plan, n_heads: int, dim: int, vdim: int, i_bi
     _check(lib().sb_mlstm_scan(_ptr(proj), plan.n_seqs, _i32(plan.seq_row0, "seq_row0"),
                                _i32(plan.seq_slot, "seq_slot"), n_heads, dim, vdim, _ptr(i_bias),
                                _ptr(f_bias), _code(i_bias.dtype), ctypes.c_float(cap),
-                               ctypes.c_float(q_scale), _ptr(state), _ptr(num), _ptr(m_row), _stream()),
+                               ctypes.c_float(q_scale), int(plan.max_new), _ptr(state), _ptr(num), _ptr(m_row),
+                               _stream()),
            "mlstm_scan")
     return num
 

@@ -63,8 +63,10 @@ class ClampedGLU(FeedForward):
     """Gated feed-forward with clamped factors: g = min(Wgate h, limit), u = clamp(Wup h, -limit,
     limit), y = Wdown (g * sigmoid(slope g) * (u + 1)), no biases.  `params` gives `limit`,
     `slope` and optionally `names`, the tensor names of the three matrices after the prefix.
-    Gate and up are one product over [gate rows | up rows]; its float32 rows go through the
-    activation kernel, which writes the activation dtype once."""
+    Gate and up are one product over the fused matrix that `interleave_gate_up` makes when the
+    intermediate size allows it (a multiple of `ops.SWIGLU_BLOCK`): the tcgen05 product applies the
+    activation in its epilogue; where another product kernel runs, its float32 rows go through
+    the activation kernel.  Other sizes keep [gate rows | up rows] and the activation kernel."""
 
     def __init__(self, spec, dtype, device):
         from ..config.specs import ConfigError
@@ -87,15 +89,20 @@ class ClampedGLU(FeedForward):
         gate, up = get(p + g), get(p + u)
         if gate.dtype != up.dtype:
             gate, up = gate.float(), up.float()
-        self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
+        self.interleaved = self.spec.intermediate % ops.SWIGLU_BLOCK == 0
+        self.w_gate_up = interleave_gate_up(gate, up) if self.interleaved else \
+            torch.cat([gate, up], dim=0).contiguous()
         self.w_down = get(p + dn)
 
     def forward(self, h, ctx, residual=None):
         rows, ff = h.shape[0], self.spec.intermediate
-        gu = torch.empty((rows, 2 * ff), dtype=torch.float32, device=h.device)
-        ops.linear(h, self.w_gate_up, gu)
         t = torch.empty((rows, ff), dtype=self.dtype, device=h.device)
-        ops.glu_clamped(gu, self.limit, self.slope, t)
+        if self.interleaved:
+            ops.linear(h, self.w_gate_up, t, ops.EPI_SWIGLU, gate=(self.limit, self.slope))
+        else:
+            gu = torch.empty((rows, 2 * ff), dtype=torch.float32, device=h.device)
+            ops.linear(h, self.w_gate_up, gu)
+            ops.glu_clamped(gu, self.limit, self.slope, t)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
         return ctx.linear(t, self.w_down, out,

@@ -17,8 +17,9 @@ from zolulix_util import CONFIGS, latent, layer, model, recur, tokens, write_mod
 pytestmark = pytest.mark.gpu
 # The largest root mean square of a row's difference, over the root mean square of the whole
 # reference (a request's logits).  The plain implementation is float64; bfloat16 rounds to 2^-9.
-# Measured on a B200 over the whole models below: float32 9.5e-6; bfloat16 stays below 5e-2
-# (activations and weights rounded to 2^-9 through sandwiched norms).
+# Measured on a B200 over the whole models below: float32 9.2e-6; bfloat16 2e-2 to 4e-2 for most
+# requests and cuts, 8.2e-2 for the worst (activations and weights rounded to 2^-9 pass through
+# two norms per sublayer; what kernel a cut's products run on moves the rounding).
 TOL = {"float32": 3e-5, "bfloat16": 1.2e-1}
 DTYPES = ["float32", "bfloat16"]
 SEEN = {}
@@ -121,14 +122,14 @@ def test_clamped_gate_activation():
 
 def test_head_linear():
     g = torch.Generator().manual_seed(4)
-    rows, heads, N, K = 37, 3, 70, 19
-    x = torch.randn(rows, heads, K + 5, generator=g)           # a head's K values sit in a longer stretch
-    w = torch.randn(heads, N, K, generator=g)
-    ref = torch.einsum("rhk,hnk->rhn", x[..., 2:2 + K].double(), w.double())
-    out = torch.zeros(rows, heads, N + 3, device="cuda")
-    ops.head_linear(x.cuda(), 2, heads * (K + 5), K + 5, w.cuda(), out, 1, heads * (N + 3), N + 3, rows)
-    assert rel_err(out[..., 1:1 + N], ref) < 1e-6
-    assert float(out[..., 0].abs().max()) == 0.0 and float(out[..., N + 1:].abs().max()) == 0.0
+    for rows, heads, N, K in ((37, 3, 70, 19), (1, 2, 9, 100), (8, 5, 33, 40), (9, 1, 64, 16)):   # few rows: a kernel of their own
+        x = torch.randn(rows, heads, K + 5, generator=g)       # a head's K values sit in a longer stretch
+        w = torch.randn(heads, N, K, generator=g)
+        ref = torch.einsum("rhk,hnk->rhn", x[..., 2:2 + K].double(), w.double())
+        out = torch.zeros(rows, heads, N + 3, device="cuda")
+        ops.head_linear(x.cuda(), 2, heads * (K + 5), K + 5, w.cuda(), out, 1, heads * (N + 3), N + 3, rows)
+        assert rel_err(out[..., 1:1 + N], ref) < 1e-6
+        assert float(out[..., 0].abs().max()) == 0.0 and float(out[..., N + 1:].abs().max()) == 0.0
 
 
 # ------------------------------------------------------------------ mechanisms alone: one-layer models
@@ -169,7 +170,7 @@ def test_whole_prompt_decoding_and_portions(folders, engines, name, dtype):
         got = run_cuts(engine, toks, cuts)
         assert model_err(got, ref, dtype) < TOL[dtype], cuts
         if dtype == "float32":
-            assert rel_err(got, whole) < 2e-6, cuts
+            assert rel_err(got, whole) < 1e-5, cuts       # rounding: few rows run other kernels
     engine.cache.check()
     assert engine.free_pages() == engine.cache.n_pages
 
@@ -191,7 +192,7 @@ def test_unequal_batch_equals_each_alone_and_slots_are_reused(folders, engines, 
     alone = [run_cuts(engine, r, [k] + [1] * (len(r) - k)) for r, k in zip(reqs, [1, 40, 100, 23])]
     if dtype == "float32":
         for o, a in zip(outs, alone):
-            assert rel_err(o, a) < 2e-6
+            assert rel_err(o, a) < 1e-5
     # a sequence that ends early gives its slot to a new one while the others go on
     a, b = engine.open(), engine.open()
     engine.step([(a, reqs[1][:30], []), (b, reqs[2][:50], [])])
