@@ -520,7 +520,7 @@ def run_zolulix(args) -> int:
         wide = rank + rd
         proj = torch.randn(rows, H * (dim + rd) + wide, device=dev)
         cache = torch.zeros((rows + 63) // 64, 2, 1, 64, wide, device=dev, dtype=bf)
-        q_wide = torch.empty(rows, H, wide, device=dev, dtype=bf)
+        q_wide = torch.empty(1, rows, H, wide, device=dev, dtype=bf)
         inv = torch.ones(rd // 2, device=dev)
         row_seq = torch.zeros(rows, dtype=torch.int32, device=dev)
         row_pos = torch.arange(rows, dtype=torch.int32, device=dev)

@@ -45,7 +45,7 @@ CORE = {
     "sb_norm_add": ("i", "ppiipifppifpis"),
     "sb_depth_mix": ("i", "pzipiiippifpis"),
     "sb_glu_clamped": ("i", "piiffipis"),
-    "sb_latent_prep": ("i", "piiiiiipppppipifpipiis"),
+    "sb_latent_prep": ("i", "piiiiiipppppipifpipiiis"),
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),
     "sb_mlstm_scan": ("i", "pippiiippiffippps"),
     "sb_mlstm_out": ("i", "pppiiiipifpis"),

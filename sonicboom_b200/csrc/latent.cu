@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(PREP_THREADS)
 latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int rank, int rot,
                    const float* __restrict__ inv_freq, const int32_t* row_seq, const int32_t* row_pos,
                    const int32_t* page_off, const int32_t* page_ids, int page_size,
-                   const TW* __restrict__ cnorm, float eps, TC* cache, TQ* q_wide, int has_kv) {
+                   const TW* __restrict__ cnorm, float eps, TC* cache, TQ* q_wide, int q_group, int has_kv) {
   __shared__ float cs[MAX_ROT_PAIRS], sn[MAX_ROT_PAIRS];
   __shared__ float red[PREP_THREADS / 32 + 1];
   sb_pdl_launch();
@@ -59,7 +59,8 @@ latent_prep_kernel(const float* proj, int ld, int n_heads, int dim, int rd, int 
       const int i = d >> 1;
       v = (d & 1) ? sb_rot_hi(qr[d - 1], qr[d], cs[i], sn[i]) : sb_rot_lo(qr[d], qr[d + 1], cs[i], sn[i]);
     }
-    q_wide[((size_t)t * n_heads + h) * wide + rank + d] = sb_from_f32<TQ>(v);
+    // wide query rows lie [head group][row][head in group]: one group is [row][head]
+    q_wide[(((size_t)(h / q_group) * gridDim.x + t) * q_group + h % q_group) * wide + rank + d] = sb_from_f32<TQ>(v);
   }
   if (!has_kv) return;
   const float* lat = src + (size_t)n_heads * hw;
@@ -181,7 +182,10 @@ extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int di
                               int rot, const float* inv_freq, const int32_t* row_seq,
                               const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
                               int page_size, const void* cnorm, int cnorm_dtype, float eps, void* cache,
-                              int cache_dtype, void* q_wide, int q_dtype, int has_kv, cudaStream_t stream) {
+                              int cache_dtype, void* q_wide, int q_dtype, int q_group, int has_kv,
+                              cudaStream_t stream) {
+  if (q_group <= 0 || n_heads % q_group)
+    SB_FAIL(SB_ERR_ARG, "sb_latent_prep: groups of %d heads do not divide %d heads", q_group, n_heads);
   if (n_rows <= 0 || n_heads <= 0 || dim < 0 || rd < 0 || rank <= 0 || !proj || !q_wide || !row_pos)
     SB_FAIL(SB_ERR_ARG, "sb_latent_prep: rows=%d heads=%d dim=%d rd=%d rank=%d", n_rows, n_heads, dim, rd, rank);
   if (rot < 0 || rot % 2 || rot > rd || rot / 2 > MAX_ROT_PAIRS)
@@ -197,7 +201,7 @@ extern "C" int sb_latent_prep(const float* proj, int n_rows, int n_heads, int di
       SB_DISPATCH_DTYPE(q_dtype, TQ, {
         sb_launch<SB_K_ELEMENTWISE>(latent_prep_kernel<TW, TC, TQ>, dim3(n_rows), dim3(PREP_THREADS), 0, stream,
                                     proj, ld, n_heads, dim, rd, rank, rot, inv_freq, row_seq, row_pos, page_off,
-                                    page_ids, page_size, (const TW*)cnorm, eps, (TC*)cache, (TQ*)q_wide, has_kv);
+                                    page_ids, page_size, (const TW*)cnorm, eps, (TC*)cache, (TQ*)q_wide, q_group, has_kv);
       });
     });
   });

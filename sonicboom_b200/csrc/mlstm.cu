@@ -280,6 +280,8 @@ extern "C" int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_r
   int rc = SB_OK;
 #define SB_SCAN(DS, NPT) rc = launch_scan<DS, NPT, TB>(n_seqs, tc, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, i_bias, f_bias, cap, q_scale, state, num, m_row)
   SB_DISPATCH_DTYPE(bias_dtype, TB, {
+    // 16 lanes a column up to 256 values: with 32 lanes the exchanges cost more than the warps gain
+    // (a 2,048-token prompt at dim 128: 472 to 931 us against 490 to 627 us, one token 25 to 38 us against 15 to 20 us)
     if (dim <= 16) SB_SCAN(16, 1);
     else if (dim <= 32) SB_SCAN(16, 2);
     else if (dim <= 64) SB_SCAN(16, 4);

@@ -161,14 +161,15 @@ int sb_glu_clamped(const float* gu, int n_rows, int ff, float limit, float alpha
 /* ---- attention over a cached latent ----
  * proj[r] = [n_heads x (dim | rd) | rank | rd] (the last two only with has_kv).  Rotates the first
  * `rot` values of every rd part in interleaved pairs (2i, 2i + 1) by float(pos) * inv_freq[i];
- * writes each head's rotated part to q_wide[r, h, rank : rank + rd]; with has_kv, RMS-norms the
+ * writes each head's rotated part to q_wide[r, h, rank : rank + rd] (q_wide lies [head group][row][head
+ * in group][rank + rd] with groups of q_group heads; q_group = n_heads is [row][head]); with has_kv, RMS-norms the
  * latent (weight cnorm, eps) and writes the page row of the position: key plane [latent | rotated
  * key part], value plane [latent | zeros].  The cache entry has one head of size rank + rd. */
 int sb_latent_prep(const float* proj, int n_rows, int n_heads, int dim, int rd, int rank, int rot,
                    const float* inv_freq, const int32_t* row_seq, const int32_t* row_pos,
                    const int32_t* page_off, const int32_t* page_ids, int page_size, const void* cnorm,
                    int cnorm_dtype, float eps, void* cache, int cache_dtype, void* q_wide, int q_dtype,
-                   int has_kv, sb_stream_t stream);
+                   int q_group, int has_kv, sb_stream_t stream);
 /* out[r * out_ld + h * out_hs + n] = sum_k in[r * in_ld + h * in_hs + k] * W[(h * N + n) * K + k] */
 int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, const void* W, int w_dtype,
                    int n_rows, int n_heads, int N, int K, void* out, int out_dtype, size_t out_ld,

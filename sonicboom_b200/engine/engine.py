@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from ..cache.kv import Cache
+from ..cache.kv import PAGE_SIZE, Cache
 from .step import StepEntry, step
 
 
@@ -12,6 +12,8 @@ class Engine:
 
     `max_tokens` is the most tokens live sequences may hold together, each sequence's count
     rounded up to a whole cache page (64 tokens); it sizes the cache."""
+
+    PAGE_SIZE = PAGE_SIZE
 
     def __init__(self, model, max_tokens: int, n_slots: int | None = None):
         self.model = model

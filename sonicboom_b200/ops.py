@@ -18,6 +18,7 @@ F32, BF16 = 0, 1
 EPI_NONE, EPI_BIAS, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 SWIGLU_BLOCK = 8                 # rows of gate and up alternate in blocks of this many
 SKINNY_MAX_ROWS = 64             # bfloat16 products of at most this many rows stream the weights
+DECODE_ATTENTION_ROWS = 16       # query rows (new tokens x heads) of one key/value head that the split decode attention takes
 
 
 class KernelError(RuntimeError):
@@ -649,16 +650,18 @@ def glu_clamped(gate_up: torch.Tensor, limit: float, slope: float, out: torch.Te
 def latent_prep(proj: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, rotary_dim: int,
                 inv_freq: torch.Tensor, row_seq, row_pos, page_off, page_ids, page_size: int,
                 cnorm: torch.Tensor | None, eps: float, cache: torch.Tensor | None,
-                q_wide: torch.Tensor) -> torch.Tensor:
+                q_wide: torch.Tensor, q_group: int = 0) -> torch.Tensor:
     """Finishes the fused projection rows [heads x (dim | rot_dim) | rank | rot_dim] (the last two
     only when `cache` is given): rotation in interleaved pairs, the latent's RMS norm, the cache
     write (key plane [latent | key part], value plane [latent | 0]), and every head's rotated
-    part into q_wide[:, :, rank:]."""
+    part into q_wide[:, :, rank:].  With `q_group` (a divisor of the heads) q_wide lies
+    [head group, row, head in group, rank + rot_dim]."""
     n = proj.shape[0]
+    q_group = q_group or n_heads
     has_kv = cache is not None
     assert proj.dtype == torch.float32
     assert proj.shape[1] == n_heads * (dim + rot_dim) + ((rank + rot_dim) if has_kv else 0)
-    assert tuple(q_wide.shape) == (n, n_heads, rank + rot_dim)
+    assert n_heads % q_group == 0 and q_wide.numel() == n * n_heads * (rank + rot_dim)
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() >= max(1, rotary_dim // 2)
     _check(lib().sb_latent_prep(
         _ptr(proj), n, n_heads, dim, rot_dim, rank, rotary_dim, _ptr(inv_freq),
@@ -667,7 +670,7 @@ def latent_prep(proj: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: 
         _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size,
         _ptr(cnorm) if has_kv else _ptr(None), _code(cnorm.dtype) if has_kv else 0, ctypes.c_float(eps),
         _ptr(cache), _code(cache.dtype) if has_kv else 0, _ptr(q_wide), _code(q_wide.dtype),
-        1 if has_kv else 0, _stream()), "latent_prep")
+        q_group, 1 if has_kv else 0, _stream()), "latent_prep")
     return q_wide
 
 

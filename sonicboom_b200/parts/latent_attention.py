@@ -83,6 +83,20 @@ class LatentAttention(Mixer):
         self.w_uv = get(p + "uv").view(self.h, self.vd, self.rank).contiguous()
         self.w_o = get(p + "o")
 
+    def _heads_per_call(self, plan, storage) -> int:
+        """How many heads one attention call takes.  All of them, except when single tokens are
+        decoded with more heads than the split decode attention takes as rows of its one
+        key/value head (`ops.DECODE_ATTENTION_ROWS`): it then runs once per group of heads, the
+        largest divisor of the head count that fits, instead of handing the step to the kernel
+        for many rows, which has one block per sequence to offer.  Which kernel runs changes the
+        rounding, nothing else."""
+        limit = ops.DECODE_ATTENTION_ROWS
+        if plan.max_new != 1 or self.h <= limit or self.dtype != torch.bfloat16 or \
+                storage.dtype != torch.bfloat16 or ops.attention_lib(self.wide) is None:
+            return self.h
+        hg = max(d for d in range(1, limit + 1) if self.h % d == 0)
+        return hg if 2 * hg > limit else self.h
+
     def forward(self, h, ctx, residual=None):
         rows, plan = h.shape[0], ctx.plan
         owns = ctx.owns_cache
@@ -95,16 +109,21 @@ class LatentAttention(Mixer):
         ops.linear(h, self.w_in[:n_in], proj)
         storage = ctx.kv_storage()
         g = plan.groups[ctx.kv_group()]
-        q_wide = torch.empty((rows, self.h, self.wide), dtype=self.dtype, device=h.device)
+        hg = self._heads_per_call(plan, storage)
+        n_g = self.h // hg
+        q_wide = torch.empty((n_g, rows, hg, self.wide), dtype=self.dtype, device=h.device)
         ops.latent_prep(proj, self.h, self.dim, self.rd, self.rank, self.position.rotary_dim,
                         self.position.inv_freq, plan.row_seq, plan.row_pos, g.page_off, g.page_ids,
-                        g.page_size, self.cnorm, self.eps, storage if owns else None, q_wide)
-        ops.head_linear(proj, 0, n_in, hw, self.w_ukt, q_wide, 0, self.h * self.wide, self.wide, rows)
-        z = torch.empty((rows, self.h * self.wide), dtype=self.dtype, device=h.device)
-        ops.attention(q_wide, z, plan, ctx.kv_group(), storage, self.h, 1, self.wide,
-                      self.spec.window, self.spec.scale)
+                        g.page_size, self.cnorm, self.eps, storage if owns else None, q_wide, hg)
+        z = torch.empty((n_g, rows, hg * self.wide), dtype=self.dtype, device=h.device)
         mixed = torch.empty((rows, self.h * self.vd), dtype=self.dtype, device=h.device)
-        ops.head_linear(z, 0, self.h * self.wide, self.wide, self.w_uv, mixed, 0, self.h * self.vd, self.vd, rows)
+        for i in range(n_g):
+            at, heads = i * rows * hg * self.wide, slice(i * hg, (i + 1) * hg)
+            ops.head_linear(proj, i * hg * hw, n_in, hw, self.w_ukt[heads], q_wide, at, hg * self.wide, self.wide, rows)
+            ops.attention(q_wide[i], z[i], plan, ctx.kv_group(), storage, hg, 1, self.wide,
+                          self.spec.window, self.spec.scale)
+            ops.head_linear(z, at, hg * self.wide, self.wide, self.w_uv[heads], mixed, i * hg * self.vd,
+                            self.h * self.vd, self.vd, rows)
         out = residual if residual is not None else \
             torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
         return ctx.linear(mixed, self.w_o, out, ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,

@@ -136,7 +136,17 @@ def test_head_linear():
 ONE_LAYER = {
     "latent": model(64, 32, [layer("latent_attention", latent(2, 8, 8, 12, 24, window=11, dims=6))]),
     "latent_wide": model(64, 32, [layer("latent_attention", latent(3, 16, 16, 8, 48, window=200))]),
+    # a latent width of 128 (the tensor-memory attention kernels) and of 144; twenty heads on one
+    # key/value head (single tokens then run the kernel for many rows)
+    "latent_128": model(64, 32, [layer("latent_attention", latent(4, 32, 32, 32, 96, window=50))]),
+    "latent_20_heads": model(64, 32, [layer("latent_attention", latent(20, 8, 16, 8, 128, window=70))]),
+    # widths and inner sizes that are no multiple of 8: the plain products in both dtypes
+    "odd_sizes": model(61, 44, [layer("latent_attention", latent(3, 12, 4, 7, 20, window=30), ff=20, limit=0.9),
+                                layer("mlstm", recur(3, 10, 7), ff=36, limit=1.1)]),
     "mlstm": model(64, 32, [layer("mlstm", recur(2, 16, 9, cap=6.0))]),
+    # key sizes served by 16 x 16 and by 32 lanes a column
+    "mlstm_dim_200": model(64, 32, [layer("mlstm", recur(1, 200, 17))]),
+    "mlstm_dim_300": model(64, 32, [layer("mlstm", recur(2, 300, 33))]),
     "mlstm_any_dim": model(64, 32, [layer("mlstm", recur(1, 20, 130, cap=20.0))]),
     "ff": model(64, 32, [layer("mlstm", recur(1, 16, 24)), layer("mlstm", recur(1, 16, 24), ff=24, limit=0.3)]),
 }
