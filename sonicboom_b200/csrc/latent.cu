@@ -147,6 +147,75 @@ head_linear_kernel(const TI* in, size_t in_ld, size_t in_hs, const TW* __restric
   }
 }
 
+// The same on tensor cores for bfloat16 weights and outputs at many rows: mma.sync m16n8k16 with
+// float32 accumulation, operands read from global memory straight into fragments (a float32
+// input is rounded to bfloat16 on the way, as every product's activation is).  A warp owns 32
+// rows x 64 outputs of one head; K is a multiple of 16, N even, and every offset even.
+constexpr int HM_WARPS = 4, HM_ROWS = 32 * HM_WARPS, HM_COLS = 64;
+
+__device__ __forceinline__ uint32_t pack2(const float* p) {
+  const float2 f = *reinterpret_cast<const float2*>(p);
+  __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+  return *reinterpret_cast<uint32_t*>(&b);
+}
+__device__ __forceinline__ uint32_t pack2(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+
+template <typename TI>
+__global__ void __launch_bounds__(HM_WARPS * 32)
+head_linear_mma_kernel(const TI* in, size_t in_ld, size_t in_hs, const __nv_bfloat16* __restrict__ W, int n_rows,
+                       int N, int K, __nv_bfloat16* out, size_t out_ld, size_t out_hs) {
+  sb_pdl_launch();
+  sb_pdl_wait();
+  const int h = blockIdx.z, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int r0 = blockIdx.x * HM_ROWS + warp * 32, n0 = blockIdx.y * HM_COLS;
+  const TI* a = in + (size_t)h * in_hs;
+  const __nv_bfloat16* w = W + (size_t)h * N * K;
+  float acc[2][8][4] = {};
+  for (int k0 = 0; k0 < K; k0 += 16) {
+    uint32_t af[2][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt) {
+      const int ra = r0 + mt * 16 + gid, rb = ra + 8;
+      const TI* pa = a + (size_t)ra * in_ld + k0 + tig * 2;
+      const TI* pb = a + (size_t)rb * in_ld + k0 + tig * 2;
+      af[mt][0] = ra < n_rows ? pack2(pa) : 0u;
+      af[mt][1] = rb < n_rows ? pack2(pb) : 0u;
+      af[mt][2] = ra < n_rows ? pack2(pa + 8) : 0u;
+      af[mt][3] = rb < n_rows ? pack2(pb + 8) : 0u;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j * 8 + gid;
+      uint32_t b0 = 0u, b1 = 0u;
+      if (n < N) {
+        const __nv_bfloat16* pw = w + (size_t)n * K + k0 + tig * 2;
+        b0 = pack2(pw);
+        b1 = pack2(pw + 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(acc[mt][j][0]), "+f"(acc[mt][j][1]), "+f"(acc[mt][j][2]), "+f"(acc[mt][j][3])
+                     : "r"(af[mt][0]), "r"(af[mt][1]), "r"(af[mt][2]), "r"(af[mt][3]), "r"(b0), "r"(b1));
+    }
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j * 8 + tig * 2;
+      if (n >= N) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int r = r0 + mt * 16 + gid + half * 8;
+        if (r < n_rows)
+          *reinterpret_cast<__nv_bfloat162*>(out + (size_t)r * out_ld + (size_t)h * out_hs + n) =
+              __floats2bfloat162_rn(acc[mt][j][half * 2], acc[mt][j][half * 2 + 1]);
+      }
+    }
+}
+
 // The same for at most HS_ROWS rows (decode): a warp per output column of a head streams that
 // column's weights once, the lanes share out K, and the rows' sums meet by shuffles.
 constexpr int HS_ROWS = 8, HS_WARPS = 8;
@@ -220,6 +289,22 @@ extern "C" int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t
     SB_FAIL(SB_ERR_ARG, "sb_head_linear: dtype codes %d %d %d", in_dtype, w_dtype, out_dtype);
   const dim3 grid((n_rows + HL_BM - 1) / HL_BM, (N + HL_BN - 1) / HL_BN, n_heads);
   const dim3 skinny((N + HS_WARPS - 1) / HS_WARPS, n_heads);
+  const size_t in_size = in_dtype == SB_F32 ? 4 : 2;
+  const bool mma = n_rows > HS_ROWS && w_dtype == SB_BF16 && out_dtype == SB_BF16 && K % 16 == 0 && N % 2 == 0 &&
+                   in_ld % 2 == 0 && in_hs % 2 == 0 && out_ld % 2 == 0 && out_hs % 2 == 0 &&
+                   (uintptr_t)in % (2 * in_size) == 0 && (uintptr_t)W % 4 == 0 && (uintptr_t)out % 4 == 0;
+  if (mma) {
+    const dim3 grid_mma((n_rows + HM_ROWS - 1) / HM_ROWS, (N + HM_COLS - 1) / HM_COLS, n_heads);
+    if (in_dtype == SB_F32)
+      sb_launch<SB_K_OTHER>(head_linear_mma_kernel<float>, grid_mma, dim3(HM_WARPS * 32), 0, stream, (const float*)in,
+                            in_ld, in_hs, (const __nv_bfloat16*)W, n_rows, N, K, (__nv_bfloat16*)out, out_ld, out_hs);
+    else
+      sb_launch<SB_K_OTHER>(head_linear_mma_kernel<__nv_bfloat16>, grid_mma, dim3(HM_WARPS * 32), 0, stream,
+                            (const __nv_bfloat16*)in, in_ld, in_hs, (const __nv_bfloat16*)W, n_rows, N, K,
+                            (__nv_bfloat16*)out, out_ld, out_hs);
+    SB_CHECK_LAUNCH("sb_head_linear");
+    return SB_OK;
+  }
   SB_DISPATCH_DTYPE(in_dtype, TI, {
     SB_DISPATCH_DTYPE(w_dtype, TW, {
       SB_DISPATCH_DTYPE(out_dtype, TO, {

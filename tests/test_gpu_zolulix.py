@@ -132,6 +132,21 @@ def test_head_linear():
         assert float(out[..., 0].abs().max()) == 0.0 and float(out[..., N + 1:].abs().max()) == 0.0
 
 
+def test_head_linear_on_tensor_cores():
+    """bfloat16 weights and outputs at many rows: float32 and bfloat16 inputs, rows and outputs that
+    end inside a tile, a head's values inside a longer stretch."""
+    g = torch.Generator().manual_seed(5)
+    for rows, heads, N, K, in_dtype in ((70, 3, 40, 32, torch.float32), (200, 2, 130, 48, torch.bfloat16),
+                                        (9, 5, 64, 16, torch.float32)):
+        x = torch.randn(rows, heads, K + 6, generator=g).to(in_dtype)
+        w = torch.randn(heads, N, K, generator=g).bfloat16()
+        ref = torch.einsum("rhk,hnk->rhn", x[..., 2:2 + K].bfloat16().double(), w.double())
+        out = torch.zeros(rows, heads, N + 4, device="cuda", dtype=torch.bfloat16)
+        ops.head_linear(x.cuda(), 2, heads * (K + 6), K + 6, w.cuda(), out, 2, heads * (N + 4), N + 4, rows)
+        assert rel_err(out[..., 2:2 + N].float(), ref) < 1e-2
+        assert float(out[..., :2].abs().max()) == 0.0 and float(out[..., N + 2:].abs().max()) == 0.0
+
+
 # ------------------------------------------------------------------ mechanisms alone: one-layer models
 ONE_LAYER = {
     "latent": model(64, 32, [layer("latent_attention", latent(2, 8, 8, 12, 24, window=11, dims=6))]),
