@@ -43,7 +43,7 @@ CORE = {
     "sb_gemm_tc5_tile_width": ("i", "iii"),
     "sb_gemm_tc5_force_width": ("v", "i"),
     "sb_norm_add": ("i", "ppiipifppifpis"),
-    "sb_depth_mix": ("i", "pzipiiippifpis"),
+    "sb_depth_mix": ("i", "pzipiiippifpipppifs"),
     "sb_glu_clamped": ("i", "piiffipis"),
     "sb_latent_prep": ("i", "piiiiiipppppipifpipiiis"),
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),

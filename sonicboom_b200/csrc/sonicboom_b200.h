@@ -148,10 +148,14 @@ int sb_norm_add(const float* y, const float* x, int n_rows, int width, const voi
                 float eps, float* out, const void* next_w, int next_w_dtype, float next_eps,
                 void* normed, int normed_dtype, sb_stream_t stream);
 /* out[r] = sum over j < n_inputs of coef[j] * planes[j * plane + r * width ...], j ascending; the
- * optional norm of the finished row as in sb_norm_add. */
-int sb_depth_mix(const float* planes, size_t plane, int n_inputs, const void* coef, int coef_dtype,
+ * optional norm of the finished row as in sb_norm_add.  With join_y non-null the last plane is made
+ * first, as sb_norm_add would: planes[n_inputs - 1][r] = join_x[r] + norm(join_y[r]) * join_w
+ * (join_w in the coefficients' dtype; join_x may be that plane). */
+int sb_depth_mix(float* planes, size_t plane, int n_inputs, const void* coef, int coef_dtype,
                  int n_rows, int width, float* out, const void* next_w, int next_w_dtype,
-                 float next_eps, void* normed, int normed_dtype, sb_stream_t stream);
+                 float next_eps, void* normed, int normed_dtype, const float* join_y,
+                 const float* join_x, const void* join_w, int join_w_dtype, float join_eps,
+                 sb_stream_t stream);
 /* gu[r] = [gate (ff) | up (ff)], or with `interleaved` blocks of 8 gates followed by the 8 up values of
  * the same outputs (ff a multiple of 8); out[r, c] = a sigmoid(alpha a) (b + 1), a = min(gate, limit),
  * b = clamp(up, -limit, limit). */

@@ -100,10 +100,14 @@ norm_add_kernel(const float* y, const float* x, int width, const TW* __restrict_
 
 constexpr int MIX_MAX = 256;       // most planes one depth mix adds up
 
+// With `join_y` the last plane is made here first: planes[n - 1][r] = join_x[r] + join_y[r] /
+// sqrt(mean(join_y[r]^2) + join_eps) * join_w (join_x may be that plane itself), so that the
+// block's last residual add and the mix that follows it are one pass over the row.
 template <int NT, int V, typename TC, typename TN, typename TO>
 __global__ void __launch_bounds__(NT)
-depth_mix_kernel(const float* planes, size_t plane, int n_inputs, const TC* __restrict__ coef,
-                 int width, float* out, const TN* __restrict__ next_w, float next_eps, TO* normed) {
+depth_mix_kernel(float* planes, size_t plane, int n_inputs, const TC* __restrict__ coef, int width, float* out,
+                 const TN* __restrict__ next_w, float next_eps, TO* normed, const float* join_y,
+                 const float* join_x, const TC* __restrict__ join_w, float join_eps) {
   __shared__ float red[NT / 32 + 1];
   __shared__ float c[MIX_MAX];
   sb_pdl_launch();
@@ -112,17 +116,38 @@ depth_mix_kernel(const float* planes, size_t plane, int n_inputs, const TC* __re
   sb_pdl_wait();
   const size_t r = blockIdx.x;
   float* o = out + r * width;
+  float inv = 0.0f;
+  if (join_y) {
+    float s = 0.0f;
+    for (int i = threadIdx.x * V; i < width; i += NT * V) {
+      const Vec<V> a = ld<V>(join_y + r * width + i);
+#pragma unroll
+      for (int j = 0; j < V; ++j) s = fmaf(a.v[j], a.v[j], s);
+    }
+    inv = 1.0f / sqrtf(block_sum<NT>(s, red) / (float)width + join_eps);
+  }
+  const int n_read = join_y ? n_inputs - 1 : n_inputs;
   float sq = 0.0f;
   for (int i = threadIdx.x * V; i < width; i += NT * V) {
-    const float* p = planes + r * width + i;
+    float* p = planes + r * width + i;
     Vec<V> v;
 #pragma unroll
     for (int j = 0; j < V; ++j) v.v[j] = 0.0f;
 #pragma unroll 4
-    for (int k = 0; k < n_inputs; ++k) {
+    for (int k = 0; k < n_read; ++k) {
       const Vec<V> a = ld<V>(p + (size_t)k * plane);
 #pragma unroll
       for (int j = 0; j < V; ++j) v.v[j] = fmaf(c[k], a.v[j], v.v[j]);
+    }
+    if (join_y) {
+      const Vec<V> a = ld<V>(join_y + r * width + i), b = ld<V>(join_x + r * width + i);
+      Vec<V> last;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        last.v[j] = b.v[j] + (a.v[j] * inv) * sb_to_f32<TC>(join_w[i + j]);
+        v.v[j] = fmaf(c[n_read], last.v[j], v.v[j]);
+      }
+      st<V>(p + (size_t)n_read * plane, last);
     }
 #pragma unroll
     for (int j = 0; j < V; ++j) sq = fmaf(v.v[j], v.v[j], sq);
@@ -194,16 +219,20 @@ extern "C" int sb_norm_add(const float* y, const float* x, int n_rows, int width
   return SB_OK;
 }
 
-extern "C" int sb_depth_mix(const float* planes, size_t plane, int n_inputs, const void* coef,
+extern "C" int sb_depth_mix(float* planes, size_t plane, int n_inputs, const void* coef,
                             int coef_dtype, int n_rows, int width, float* out, const void* next_w,
                             int next_w_dtype, float next_eps, void* normed, int normed_dtype,
-                            cudaStream_t stream) {
+                            const float* join_y, const float* join_x, const void* join_w, int join_w_dtype,
+                            float join_eps, cudaStream_t stream) {
+  if (join_y && (!join_x || !join_w || join_w_dtype != coef_dtype || !(join_eps >= 0.0f)))
+    SB_FAIL(SB_ERR_ARG, "sb_depth_mix: a joined last plane needs its stream, a norm weight of the coefficients' dtype and eps");
   if (n_rows <= 0 || width <= 0 || !planes || !coef || !out)
     SB_FAIL(SB_ERR_ARG, "sb_depth_mix: rows=%d width=%d", n_rows, width);
   if (n_inputs < 1 || n_inputs > MIX_MAX)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_depth_mix: %d inputs (1 to %d)", n_inputs, MIX_MAX);
   if (plane < (size_t)n_rows * width) SB_FAIL(SB_ERR_ARG, "sb_depth_mix: planes overlap");
-  const bool vec = width % 4 == 0 && plane % 4 == 0 && (((uintptr_t)planes | (uintptr_t)out) & 15) == 0;
+  const bool vec = width % 4 == 0 && plane % 4 == 0 &&
+                   (((uintptr_t)planes | (uintptr_t)out | (uintptr_t)join_y | (uintptr_t)join_x) & 15) == 0;
   const bool wide = n_rows <= 256 && width >= 2048;
   if (!sb_valid_dtype(coef_dtype) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_depth_mix: dtype codes %d %d %d", coef_dtype, next_w_dtype, normed_dtype);
@@ -211,7 +240,7 @@ extern "C" int sb_depth_mix(const float* planes, size_t plane, int n_inputs, con
     SB_DISPATCH_NEXT(normed, next_w_dtype, TN, {
       SB_DISPATCH_NEXT(normed, normed_dtype, TO, {
         SB_ROW_LAUNCH(depth_mix_kernel, TC, planes, plane, n_inputs, (const TC*)coef, width, out, (const TN*)next_w,
-                      next_eps, (TO*)normed);
+                      next_eps, (TO*)normed, join_y, join_x, (const TC*)join_w, join_eps);
       });
     });
   });

@@ -104,12 +104,18 @@ class DecoderModel:
             if streams is not None:
                 if getattr(block, "writes_block_out", False):
                     ctx.block_out = streams[i + 1]
+                    # the block may run the mix together with its last residual add
+                    ctx.block_mix = (mix, streams, next_norm) if mix is not None and hasattr(mix, "joins") else None
                 elif x.data_ptr() == streams[i].data_ptr():
                     x = ops.depth_mix(streams[i:i + 1], 1, self._one(), torch.empty_like(x))   # the block may overwrite its input
             with ops.trace_range(f"entry {i} (layer {e.layer})"):
                 x = block.forward(x, ctx)
-            ctx.block_out = None
+            ctx.block_out = ctx.block_mix = None
+            mixed, ctx.mixed_out = ctx.mixed_out, None
             if streams is None:
+                continue
+            if mixed is not None:
+                x = mixed
                 continue
             if x.data_ptr() != streams[i + 1].data_ptr():
                 ops.depth_mix(x.unsqueeze(0), 1, self._one(), streams[i + 1])

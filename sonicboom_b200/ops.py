@@ -608,6 +608,17 @@ def _next_norm_args(next_norm, width, rows):
     return _ptr(w), _code(w.dtype), ctypes.c_float(eps), _ptr(normed), _code(normed.dtype)
 
 
+def _join_args(join, coef, rows, width):
+    if join is None:
+        return _ptr(None), _ptr(None), _ptr(None), 0, ctypes.c_float(0.0)
+    y, x, w, eps = join
+    assert y.dtype == x.dtype == torch.float32 and tuple(y.shape) == tuple(x.shape) == (rows, width)
+    assert w.numel() == width
+    if w.dtype != coef.dtype:
+        raise KernelError("depth_mix: the joined norm's weight and the coefficients differ in dtype")
+    return _ptr(y), _ptr(x), _ptr(w), _code(w.dtype), ctypes.c_float(eps)
+
+
 def norm_add(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
              next_norm: tuple | None = None) -> torch.Tensor:
     """out = x + y / sqrt(mean(y^2) + eps) * weight, row by row in float32 (out may be x).
@@ -622,15 +633,18 @@ def norm_add(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
 
 
 def depth_mix(planes: torch.Tensor, n_inputs: int, coef: torch.Tensor, out: torch.Tensor,
-              next_norm: tuple | None = None) -> torch.Tensor:
-    """out = sum_j coef[j] * planes[j] over the first n_inputs planes of float32 [n, rows, width]."""
+              next_norm: tuple | None = None, join: tuple | None = None) -> torch.Tensor:
+    """out = sum_j coef[j] * planes[j] over the first n_inputs planes of float32 [n, rows, width].
+    `join` = (y, x, weight, eps) makes the last of those planes first, as `norm_add` would:
+    planes[n_inputs - 1] = x + y / sqrt(mean(y^2) + eps) * weight (x may be that plane)."""
     rows, width = out.shape
     assert planes.dtype == out.dtype == torch.float32 and planes.dim() == 3
     assert tuple(planes.shape[1:]) == (rows, width) and 1 <= n_inputs <= planes.shape[0]
     assert coef.numel() == n_inputs
     _check(lib().sb_depth_mix(_ptr(planes), ctypes.c_size_t(rows * width), n_inputs, _ptr(coef),
                               _code(coef.dtype), rows, width, _ptr(out),
-                              *_next_norm_args(next_norm, width, rows), _stream()), "depth_mix")
+                              *_next_norm_args(next_norm, width, rows), *_join_args(join, coef, rows, width),
+                              _stream()), "depth_mix")
     return out
 
 

@@ -51,6 +51,8 @@ class StepContext:
     after_block_weights: Optional[torch.Tensor] = None  # what the entry that runs next streams first, if it asks late
     _normed: Optional[tuple] = None        # (norm, rows, normed rows) of the last `linear` that had one
     block_out: Optional[torch.Tensor] = None            # where the caller wants the running block's result (a block may ignore it)
+    block_mix: Optional[tuple] = None                   # (depth mix, streams, next norm) the caller runs on that result; a block may run it with its last add
+    mixed_out: Optional[torch.Tensor] = None            # what that depth mix handed on, when the block ran it
 
     def linear(self, a, w, out, epilogue, residual=None, bias=None, act_dtype=None):
         """ops.linear into float32 `out`; when `next_norm` is an RMS norm with a plain weight,

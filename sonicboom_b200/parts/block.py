@@ -55,7 +55,8 @@ class SandwichNormBlock(Block):
     (without a feed-forward the block's result is x1).  The normed sublayer result joins the
     stream in one kernel (`ops.norm_add`), which also writes the norm that comes next when that is
     known: the feed-forward's own input norm, or the next entry's first norm
-    (`ctx.after_block_norm`).  When the caller names a place for the result (`ctx.block_out`), the
+    (`ctx.after_block_norm`).  When the caller is going to run a depth mix on the result
+    (`ctx.block_mix`), the last add and that mix are one kernel.  When the caller names a place for the result (`ctx.block_out`), the
     block writes there and leaves its input as it was; else it overwrites its input."""
     writes_block_out = True
 
@@ -106,8 +107,28 @@ class SandwichNormBlock(Block):
         ctx.keep_normed(then, out, normed)
         return out
 
+    def _join_and_mix(self, y, x, post, out, ctx, mix, streams, next_norm):
+        """The block's last add and the depth mix the caller would run on its result, in one kernel."""
+        import torch
+        w, eps = post.as_rms()
+        mixed = torch.empty_like(out)
+        rms = next_norm.as_rms() if next_norm is not None else None
+        normed = torch.empty(out.shape, dtype=self.dtype, device=out.device) if rms is not None else None
+        mix.forward(streams, mixed, (rms[0], rms[1], normed) if rms is not None else None, join=(y, x, w, eps))
+        if rms is not None:
+            ctx.keep_normed(next_norm, mixed, normed)
+        ctx.mixed_out = mixed
+        return out
+
+    def _last_join(self, y, x, post, out, ctx, after, mix):
+        if mix is not None and mix[1][mix[0].spec.n_inputs - 1].data_ptr() == out.data_ptr() \
+                and mix[0].joins(post.as_rms()[0]):
+            return self._join_and_mix(y, x, post, out, ctx, *mix)
+        return self._join(y, x, post, out, ctx, after)
+
     def forward(self, x, ctx):
         out, ctx.block_out = (ctx.block_out if ctx.block_out is not None else x), None
+        mix, ctx.block_mix, ctx.mixed_out = ctx.block_mix, None, None
         after, ctx.after_block_norm, ctx.after_block_weights = ctx.after_block_norm, None, None
         h = ctx.take_normed(self.mixer_norm, x)
         if h is None:
@@ -115,11 +136,11 @@ class SandwichNormBlock(Block):
         ctx.next_norm = ctx.next_weights = None      # the post norm, not a norm of the stream, follows the product
         y = self.mixer.forward(h, ctx)
         if self.feed_forward is None:
-            return self._join(y, x, self.mixer_post_norm, out, ctx, after)
+            return self._last_join(y, x, self.mixer_post_norm, out, ctx, after, mix)
         x1 = self._join(y, x, self.mixer_post_norm, out, ctx, self.feed_forward_norm)
         f = ctx.take_normed(self.feed_forward_norm, x1)
         if f is None:
             f = self.feed_forward_norm.forward(x1, self.dtype)
         ctx.next_norm = ctx.next_weights = None
         y = self.feed_forward.forward(f, ctx)
-        return self._join(y, x1, self.feed_forward_post_norm, out, ctx, after)
+        return self._last_join(y, x1, self.feed_forward_post_norm, out, ctx, after, mix)

@@ -24,6 +24,12 @@ class WeightedDepthSum(Part):
     def bind(self, get):
         self.coef = get(self.spec.tensor)
 
-    def forward(self, streams, out, next_norm=None):
-        """out = sum_j coef[j] * streams[j] over the first n_inputs streams."""
-        return ops.depth_mix(streams, self.spec.n_inputs, self.coef, out, next_norm)
+    def joins(self, weight) -> bool:
+        """Whether `forward` can also make the last stream from a block's last sublayer result
+        (`join`): the kernel reads the norm's weight as it reads the coefficients."""
+        return weight.dtype == self.coef.dtype
+
+    def forward(self, streams, out, next_norm=None, join=None):
+        """out = sum_j coef[j] * streams[j] over the first n_inputs streams.  `join` = (y, x,
+        weight, eps): the last stream is x + norm(y) * weight and is written first."""
+        return ops.depth_mix(streams, self.spec.n_inputs, self.coef, out, next_norm, join)

@@ -109,6 +109,24 @@ def test_depth_mix():
                            ops.depth_mix(streams.cuda(), n, coef.bfloat16().cuda(), torch.empty_like(out)))
 
 
+def test_depth_mix_with_the_last_add():
+    """The block's last residual add made inside the mix: the last stream is x + norm(y) * g."""
+    g = torch.Generator().manual_seed(6)
+    for rows, width, n in ((3, 40, 2), (300, 64, 5), (2, 2052, 9)):
+        streams = torch.randn(n, rows, width, generator=g)
+        y = torch.randn(rows, width, generator=g) * 2
+        coef, w2 = torch.randn(n, generator=g), torch.randn(width, generator=g)
+        gw = torch.full((width,), -0.8)
+        last = streams[n - 1].double() + pz.rms(y.double(), 1e-5) * (-0.8)
+        ref = pz.depth_sum(list(streams[:n - 1].double()) + [last], coef.double())
+        dev = streams.cuda()
+        out, normed = torch.empty(rows, width, device="cuda"), torch.empty(rows, width, device="cuda")
+        ops.depth_mix(dev, n, coef.cuda(), out, (w2.cuda(), 1e-6, normed), join=(y.cuda(), dev[n - 1], gw.cuda(), 1e-5))
+        assert rel_err(out, ref) < 1e-6 and rel_err(dev[n - 1], last) < 1e-6
+        assert rel_err(normed, pz.rms(ref, 1e-6) * w2.double()) < 1e-5
+        assert torch.equal(dev[:n - 1].cpu(), streams[:n - 1])
+
+
 def test_clamped_gate_activation():
     g = torch.Generator().manual_seed(3)
     gu = torch.randn(6, 2 * 37, generator=g) * 3
