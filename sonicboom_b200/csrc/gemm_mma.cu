@@ -66,7 +66,7 @@ template <int NT, typename TO>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int K,
                    int epilogue, const void* __restrict__ bias, int bias_dtype,
-                   const float* residual, TO* out) {
+                   const float* residual, TO* out, float gate_limit, float gate_slope) {
   __shared__ float partial[SK_WARPS][NT][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int m0 = blockIdx.x * 16;
@@ -134,7 +134,9 @@ gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int 
       float up = 0.0f;
 #pragma unroll
       for (int w = 0; w < SK_WARPS; ++w) up += partial[w][nt][src_lane][reg + 2];
-      out[(size_t)b * (N / 2) + (m0 / 2 + r)] = sb_from_f32<TO>(sb_silu(v) * up);
+      // gate_limit > 0: the clamped form a sigmoid(slope a) (b + 1) instead of silu(gate) * up
+      out[(size_t)b * (N / 2) + (m0 / 2 + r)] = sb_from_f32<TO>(
+          gate_limit > 0.0f ? sb_glu_clamped(v, up, gate_limit, gate_slope) : sb_silu(v) * up);
       continue;
     }
     if (n >= N) continue;
@@ -149,11 +151,11 @@ gemm_skinny_kernel(const bf16* X, const bf16* __restrict__ W, int M, int N, int 
 template <int NT>
 int launch_skinny(const bf16* X, const bf16* W, int M, int N, int K, int epilogue,
                   const void* bias, int bias_dtype, const float* residual, void* out,
-                  int out_dtype, cudaStream_t stream) {
+                  int out_dtype, float gate_limit, float gate_slope, cudaStream_t stream) {
   const int blocks = (N + 15) / 16;
   SB_DISPATCH_DTYPE(out_dtype, TO, {
     sb_launch<SB_K_SKINNY>(gemm_skinny_kernel<NT, TO>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream,
-        X, W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out);
+        X, W, M, N, K, epilogue, bias, bias_dtype, residual, (TO*)out, gate_limit, gate_slope);
   });
   SB_CHECK_LAUNCH("sb_gemm_skinny");
   return SB_OK;
@@ -315,23 +317,39 @@ int check_bf16_product(const char* who, int a_dtype, int w_dtype, int K, const v
 
 }  // namespace
 
-extern "C" int sb_gemm_skinny(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
-                              int K, int epilogue, const void* bias, int bias_dtype,
-                              const float* residual, void* out, int out_dtype,
-                              cudaStream_t stream) {
+static int gemm_skinny(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
+                       int epilogue, const void* bias, int bias_dtype, const float* residual, void* out,
+                       int out_dtype, float gate_limit, float gate_slope, cudaStream_t stream) {
   if (int rc = sb_check_linear_args("sb_gemm_skinny", M, N, K, epilogue, bias, residual, out_dtype))
     return rc;
   if (int rc = check_bf16_product("sb_gemm_skinny", a_dtype, w_dtype, K, A, W)) return rc;
   if (M > 64) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_gemm_skinny: at most 64 rows, got %d", M);
   if (!sb_valid_dtype(out_dtype)) SB_FAIL(SB_ERR_ARG, "sb_gemm_skinny: out dtype %d", out_dtype);
   const bf16 *x = (const bf16*)A, *w = (const bf16*)W;
-  if (M <= 8)
-    return launch_skinny<1>(x, w, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, stream);
-  if (M <= 16)
-    return launch_skinny<2>(x, w, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, stream);
-  if (M <= 32)
-    return launch_skinny<4>(x, w, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, stream);
-  return launch_skinny<8>(x, w, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, stream);
+#define SB_SKINNY(NT) launch_skinny<NT>(x, w, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, gate_limit, gate_slope, stream)
+  if (M <= 8) return SB_SKINNY(1);
+  if (M <= 16) return SB_SKINNY(2);
+  if (M <= 32) return SB_SKINNY(4);
+  return SB_SKINNY(8);
+#undef SB_SKINNY
+}
+
+extern "C" int sb_gemm_skinny(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                              int K, int epilogue, const void* bias, int bias_dtype,
+                              const float* residual, void* out, int out_dtype,
+                              cudaStream_t stream) {
+  return gemm_skinny(A, a_dtype, W, w_dtype, M, N, K, epilogue, bias, bias_dtype, residual, out, out_dtype, 0.0f,
+                     1.0f, stream);
+}
+
+// The gated product (SB_EPI_SWIGLU layout) with the clamped activation a sigmoid(slope a) (b + 1),
+// a = min(gate, limit), b = clamp(up, -limit, limit).
+extern "C" int sb_gemm_skinny_gated(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,
+                                    int K, void* out, int out_dtype, float gate_limit, float gate_slope,
+                                    cudaStream_t stream) {
+  if (!(gate_limit > 0.0f)) SB_FAIL(SB_ERR_ARG, "sb_gemm_skinny_gated: limit %g must be positive", gate_limit);
+  return gemm_skinny(A, a_dtype, W, w_dtype, M, N, K, SB_EPI_SWIGLU, nullptr, 0, nullptr, out, out_dtype,
+                     gate_limit, gate_slope, stream);
 }
 
 extern "C" int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N,

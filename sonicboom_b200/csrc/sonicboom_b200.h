@@ -117,6 +117,10 @@ int sb_gemm_plain(const void* A, int a_dtype, const void* W, int w_dtype, int M,
 int sb_gemm_skinny(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
                    int epilogue, const void* bias, int bias_dtype, const float* residual,
                    void* out, int out_dtype, sb_stream_t stream);
+/* sb_gemm_skinny with SB_EPI_SWIGLU's layout and the clamped gated activation (see SbLinearExtras). */
+int sb_gemm_skinny_gated(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
+                         void* out, int out_dtype, float gate_limit, float gate_slope,
+                         sb_stream_t stream);
 int sb_gemm_tiled(const void* A, int a_dtype, const void* W, int w_dtype, int M, int N, int K,
                   int epilogue, const void* bias, int bias_dtype, const float* residual,
                   void* out, int out_dtype, sb_stream_t stream);

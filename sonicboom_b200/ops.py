@@ -173,7 +173,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
 
     `gate` = (limit, slope) with EPI_SWIGLU makes the gated epilogue the clamped form
     a * sigmoid(slope a) * (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit): inside the
-    tcgen05 kernel where that runs, else as the plain product followed by `glu_clamped`.
+    tcgen05 and the weight-streaming kernels where they run, else as the plain product followed
+    by `glu_clamped`.
 
     `norm` = (weight, eps, norm_out) also writes norm_out = rmsnorm(out, weight, eps) [M,N]
     (out must be float32): in the kernel that finishes the product where one does (the split-K
@@ -200,8 +201,13 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = 
             raise KernelError("linear: a float32 activation needs float32 weights")
     if gate is not None:
         assert epilogue == EPI_SWIGLU and N % (2 * SWIGLU_BLOCK) == 0
-        fused = a.dtype == torch.bfloat16 and kernel in ("auto", "tc5") and K % 8 == 0 and \
-            (kernel == "tc5" or _pick_kernel(M, N, K, a.device) == "tc5")
+        picked = kernel if kernel != "auto" else _pick_kernel(M, N, K, a.device)
+        fused = a.dtype == torch.bfloat16 and K % 8 == 0 and picked == "tc5"
+        if a.dtype == torch.bfloat16 and K % 8 == 0 and picked == "skinny" and M <= SKINNY_MAX_ROWS:
+            _check(lib().sb_gemm_skinny_gated(_ptr(a), BF16, _ptr(w), BF16, M, N, K, _ptr(out), _code(out.dtype),
+                                              ctypes.c_float(gate[0]), ctypes.c_float(gate[1]), _stream()),
+                   "linear (weight-streaming kernel, gated)")
+            return out
         if not fused:
             gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
             linear(a, w, gu, EPI_NONE, kernel=kernel)

@@ -138,6 +138,28 @@ def test_clamped_gate_activation():
     assert float(gu[:, :37].max()) > 1.0 and float(gu[:, 37:].min()) < -1.0      # the clamps were in play
 
 
+def test_gated_product_with_clamped_activation():
+    """One product over interleaved gate and up rows whose epilogue applies the clamped activation:
+    the weight-streaming kernel (few rows), the tcgen05 kernel in its decode and its many-rows
+    forms, and the plain product followed by the activation kernel (float32)."""
+    from sonicboom_b200.parts.feedforward import interleave_gate_up
+    g = torch.Generator().manual_seed(8)
+    K, ff, limit, slope = 96, 80, 0.6, 1.702
+    gate, up = torch.randn(ff, K, generator=g) * 0.2, torch.randn(ff, K, generator=g) * 0.2
+    for dtype in (torch.bfloat16, torch.float32):
+        wg, wu = gate.to(dtype), up.to(dtype)
+        w = interleave_gate_up(wg, wu).cuda()
+        for rows in (3, 8, 40, 300):
+            x = (torch.randn(rows, K, generator=g)).to(dtype)
+            a = (x.double() @ wg.double().T).clamp(max=limit)
+            b = (x.double() @ wu.double().T).clamp(-limit, limit)
+            ref = a * torch.sigmoid(slope * a) * (b + 1)
+            out = torch.empty(rows, ff, device="cuda", dtype=dtype)
+            ops.linear(x.cuda(), w, out, ops.EPI_SWIGLU, gate=(limit, slope))
+            assert rel_err(out.float(), ref) < (1e-2 if dtype == torch.bfloat16 else 1e-6), (dtype, rows)
+    assert float(a.max()) == limit and float(b.min()) == -limit            # the clamps were in play
+
+
 def test_head_linear():
     g = torch.Generator().manual_seed(4)
     for rows, heads, N, K in ((37, 3, 70, 19), (1, 2, 9, 100), (8, 5, 33, 40), (9, 1, 64, 16)):   # few rows: a kernel of their own
