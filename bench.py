@@ -556,7 +556,7 @@ def run_zolulix(args) -> int:
         Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
         Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
         rproj = torch.randn(rows, 2 * rh * (rdim + rvd + 1), device=dev) * 0.1
-        state = torch.zeros(Plan.n_seqs, rh, rvd + 1, rdim + 1, device=dev)
+        state = torch.zeros(Plan.n_seqs, rh, rvd + 1, (rdim + 4) // 4 * 4, device=dev)
         num, m_row = torch.empty(rows, rh, rvd + 1, device=dev), torch.empty(rows, rh, device=dev)
         bi = torch.zeros(rh, device=dev, dtype=bf)
         rec(f"mlstm_scan ({Plan.n_seqs} sequence(s) of {per})",

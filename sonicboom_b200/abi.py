@@ -48,7 +48,7 @@ CORE = {
     "sb_glu_clamped": ("i", "piiffipis"),
     "sb_latent_prep": ("i", "piiiiiipppppipifpipiiis"),
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),
-    "sb_mlstm_scan": ("i", "pippiiippiffippps"),
+    "sb_mlstm_scan": ("i", "pippiiippiffipipps"),
     "sb_mlstm_out": ("i", "pppiiiipifpis"),
     "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
     "sb_sample_params_size": ("i", ""),

@@ -14,7 +14,8 @@
 // lanes of a warp (lane s keeps d = s, s + DS, ... in registers), the lanes' partial sums of
 // S_t^T q_t meet by shuffles, and columns never meet: every column also keeps a copy of m, so
 // that no column reads what another one writes.  State per slot: float32 [heads, vdim + 1,
-// dim + 1], a column's dim values side by side and its copy of m after them.  The walk is the
+// col_stride], a column's dim values side by side and its copy of m after them (col_stride is
+// dim + 1 or more; a multiple of 4 lets runs of four values travel in 16-byte accesses).  The walk is the
 // recurrence itself, token by token in float32, for prompts, portions of prompts and single
 // tokens alike, so a position's result does not depend on how its sequence was cut into steps.
 // Tokens are staged in shared memory a chunk at a time; per chunk the gates are worked out by a
@@ -54,12 +55,17 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 template <int DS, int NPT, typename TB>
 __global__ void __launch_bounds__(SCAN_THREADS)
 mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int32_t* seq_slot, int H,
-                  int dim, int vdim, int tc, const TB* __restrict__ i_bias, const TB* __restrict__ f_bias,
+                  int dim, int vdim, int col_stride, int tc, const TB* __restrict__ i_bias, const TB* __restrict__ f_bias,
                   float cap, float q_scale, float* state, float* num, float* m_row) {
   constexpr int CPB = SCAN_THREADS / DS;   // columns per block
-  extern __shared__ float smem[];
+  // Which of a column's values lane ls keeps as S[i]: with NPT a multiple of 4, runs of four
+  // neighbours (16-byte shared-memory loads of k and q), the runs dealt out over the lanes;
+  // else every DS-th value.
+  constexpr bool VEC = NPT % 4 == 0;
+  auto d_of = [](int ls_, int i) { return VEC ? (i / 4) * (DS * 4) + ls_ * 4 + i % 4 : ls_ + DS * i; };
+  extern __shared__ __align__(16) float smem[];
   const int dim_p = DS * NPT;
-  const int stage = 2 * tc * dim_p + tc * CPB + 2 * tc;      // floats of one stage: q, k, v, x_i, x_f
+  const int stage = (2 * tc * dim_p + tc * CPB + 2 * tc + 3) & ~3;      // floats of one stage: q, k, v, x_i, x_f (16-byte steps)
   float* ig_s = smem + 2 * stage;          // [tc] log input gate, then its factor exp(i - m)
   float* fg_s = ig_s + tc;                 // [tc] log forget gate, then its factor exp(f + m' - m)
   float* m_s = fg_s + tc;                  // [tc + 1]: m before the chunk, then after each token
@@ -69,7 +75,7 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
   const int jj = blockIdx.z * CPB + c, cols = vdim + 1;
   const bool active = jj < cols;
   const int row0 = seq_row0[b], T = seq_row0[b + 1] - row0;
-  float* st = state + (((size_t)seq_slot[b] * H + h) * cols + (active ? jj : 0)) * (size_t)(dim + 1);
+  float* st = state + (((size_t)seq_slot[b] * H + h) * cols + (active ? jj : 0)) * (size_t)col_stride;
   const float bi = sb_to_f32<TB>(i_bias[h]), bf = sb_to_f32<TB>(f_bias[h]);
   const int q_off = h * dim, k_off = H * dim + h * dim, v_off = 2 * H * dim + h * vdim;
   const int i_off = 2 * H * dim + 2 * H * vdim + h, f_off = i_off + H;
@@ -114,9 +120,20 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
   load_chunk(0, 0);
   float S[NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int d = ls + DS * i;
-    S[i] = (active && d < dim) ? st[d] : 0.0f;
+  for (int g = 0; g < (VEC ? NPT / 4 : NPT); ++g) {
+    if (VEC) {                       // a run of four in one 16-byte load where it lies inside the column
+      const int d = d_of(ls, g * 4);
+      if (active && d + 3 < dim && col_stride % 4 == 0) {
+        const float4 v = *reinterpret_cast<const float4*>(st + d);
+        S[(g * 4) % NPT] = v.x; S[(g * 4 + 1) % NPT] = v.y; S[(g * 4 + 2) % NPT] = v.z; S[(g * 4 + 3) % NPT] = v.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) S[(g * 4 + e) % NPT] = (active && d + e < dim) ? st[d + e] : 0.0f;
+      }
+    } else {
+      const int d = d_of(ls, g);
+      S[g % NPT] = (active && d < dim) ? st[d] : 0.0f;
+    }
   }
   if (tid == 0) m_s[0] = st[dim];
   float m_last = 0.0f;
@@ -167,15 +184,31 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
         acc[u] = 0.0f;
         if (tt < nt) {
           const float a = fg_s[tt], bv = ig_s[tt] * v_s[tt * CPB + c];
-          const float* kt = k_s + tt * dim_p + ls;
-          const float* qt = q_s + tt * dim_p + ls;
+          const float* kt = k_s + tt * dim_p;
+          const float* qt = q_s + tt * dim_p;
           float acc1 = 0.0f;
+          if (VEC) {
 #pragma unroll
-          for (int i = 0; i < NPT; ++i) {
-            const float sv = fmaf(S[i], a, kt[DS * i] * bv);
-            S[i] = sv;
-            if (i & 1) acc1 = fmaf(sv, qt[DS * i], acc1);
-            else acc[u] = fmaf(sv, qt[DS * i], acc[u]);
+            for (int i4 = 0; i4 < NPT / 4; ++i4) {
+              const float4 kv = *reinterpret_cast<const float4*>(kt + i4 * (DS * 4) + ls * 4);
+              const float4 qv = *reinterpret_cast<const float4*>(qt + i4 * (DS * 4) + ls * 4);
+              const float k4[4] = {kv.x, kv.y, kv.z, kv.w}, q4[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float sv = fmaf(S[i4 * 4 + e], a, k4[e] * bv);
+                S[i4 * 4 + e] = sv;
+                if (e & 1) acc1 = fmaf(sv, q4[e], acc1);
+                else acc[u] = fmaf(sv, q4[e], acc[u]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < NPT; ++i) {
+              const float sv = fmaf(S[i], a, kt[ls + DS * i] * bv);
+              S[i] = sv;
+              if (i & 1) acc1 = fmaf(sv, qt[ls + DS * i], acc1);
+              else acc[u] = fmaf(sv, qt[ls + DS * i], acc[u]);
+            }
           }
           acc[u] += acc1;
         }
@@ -198,9 +231,21 @@ mlstm_scan_kernel(const float* proj, int ld, const int32_t* seq_row0, const int3
   }
   if (active) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int d = ls + DS * i;
-      if (d < dim) st[d] = S[i];
+    for (int g = 0; g < (VEC ? NPT / 4 : NPT); ++g) {
+      if (VEC) {
+        const int d = d_of(ls, g * 4);
+        if (d + 3 < dim && col_stride % 4 == 0) {
+          *reinterpret_cast<float4*>(st + d) =
+              make_float4(S[(g * 4) % NPT], S[(g * 4 + 1) % NPT], S[(g * 4 + 2) % NPT], S[(g * 4 + 3) % NPT]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (d + e < dim) st[d + e] = S[(g * 4 + e) % NPT];
+        }
+      } else {
+        const int d = d_of(ls, g);
+        if (d < dim) st[d] = S[g % NPT];
+      }
     }
     if (ls == 0) st[dim] = m_last;
   }
@@ -243,10 +288,10 @@ mlstm_out_kernel(const float* num, const float* m_row, const float* proj, int ld
 
 template <int DS, int NPT, typename TB>
 int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int ld, const int32_t* seq_row0,
-                const int32_t* seq_slot, int H, int dim, int vdim, const void* ib, const void* fb, float cap,
+                const int32_t* seq_slot, int H, int dim, int vdim, int col_stride, const void* ib, const void* fb, float cap,
                 float q_scale, float* state, float* num, float* m_row) {
   constexpr int CPB = SCAN_THREADS / DS;
-  const size_t smem = sizeof(float) * (2 * ((size_t)2 * tc * DS * NPT + (size_t)tc * CPB + 2 * tc) + 3 * tc + 1);
+  const size_t smem = sizeof(float) * (2 * ((((size_t)2 * tc * DS * NPT + (size_t)tc * CPB + 2 * tc) + 3) & ~(size_t)3) + 3 * tc + 1);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(mlstm_scan_kernel<DS, NPT, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
@@ -254,7 +299,7 @@ int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int 
   }
   const dim3 grid(n_seqs, H, (vdim + 1 + CPB - 1) / CPB);
   sb_launch<SB_K_OTHER>(mlstm_scan_kernel<DS, NPT, TB>, grid, dim3(SCAN_THREADS), smem, stream, proj, ld, seq_row0,
-                        seq_slot, H, dim, vdim, tc, (const TB*)ib, (const TB*)fb, cap, q_scale, state, num, m_row);
+                        seq_slot, H, dim, vdim, col_stride, tc, (const TB*)ib, (const TB*)fb, cap, q_scale, state, num, m_row);
   return SB_OK;
 }
 
@@ -263,7 +308,8 @@ int launch_scan(int n_seqs, int tc, cudaStream_t stream, const float* proj, int 
 extern "C" int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_row0,
                              const int32_t* seq_slot, int n_heads, int dim, int vdim, const void* i_bias,
                              const void* f_bias, int bias_dtype, float cap, float q_scale, int max_new,
-                             float* state, float* num, float* m_row, cudaStream_t stream) {
+                             float* state, int col_stride, float* num, float* m_row, cudaStream_t stream) {
+  if (col_stride < dim + 1) SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: a state column of %d values cannot hold %d + 1", col_stride, dim);
   if (n_seqs <= 0 || n_heads <= 0 || dim <= 0 || vdim <= 0 || !proj || !seq_row0 || !seq_slot || !state || !num ||
       !m_row || !i_bias || !f_bias)
     SB_FAIL(SB_ERR_ARG, "sb_mlstm_scan: seqs=%d heads=%d dim=%d vdim=%d", n_seqs, n_heads, dim, vdim);
@@ -278,7 +324,7 @@ extern "C" int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_r
   while (tc > 4 && (size_t)tc * dim * 8 > 32 * 1024) tc >>= 1;
   while (tc > 1 && tc / 2 >= max_new) tc >>= 1;            // no longer than the step's longest portion
   int rc = SB_OK;
-#define SB_SCAN(DS, NPT) rc = launch_scan<DS, NPT, TB>(n_seqs, tc, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, i_bias, f_bias, cap, q_scale, state, num, m_row)
+#define SB_SCAN(DS, NPT) rc = launch_scan<DS, NPT, TB>(n_seqs, tc, stream, proj, ld, seq_row0, seq_slot, n_heads, dim, vdim, col_stride, i_bias, f_bias, cap, q_scale, state, num, m_row)
   SB_DISPATCH_DTYPE(bias_dtype, TB, {
     // 16 lanes a column up to 256 values: with 32 lanes the exchanges cost more than the warps gain
     // (a 2,048-token prompt at dim 128: 472 to 931 us against 490 to 627 us, one token 25 to 38 us against 15 to 20 us)

@@ -185,15 +185,15 @@ int sb_head_linear(const void* in, int in_dtype, size_t in_ld, size_t in_hs, con
 
 /* ---- matrix-memory recurrence (mLSTM) ----
  * proj[r] = [q heads*dim | k heads*dim | v heads*vdim | g heads*vdim | x_i heads | x_f heads] float32.
- * state: float32 [slot, heads, vdim + 1, dim + 1] (column vdim is the normalizer; after a column's dim
- * values comes its copy of the running maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
+ * state: float32 [slot, heads, vdim + 1, col_stride] with col_stride >= dim + 1 (column vdim is the
+ * normalizer; after a column's dim values comes its copy of the running maximum).  sb_mlstm_scan walks every sequence's rows in order from its slot's state and leaves the
  * state after the last row; num [rows, heads, vdim + 1] and m_row [rows, heads] receive the
  * numerators and maxima; max_new is an upper bound of any sequence's rows in the step.  sb_mlstm_out divides, norms each head (eps), applies norm_w
  * [heads*vdim] and the gate sigmoid(g): out [rows, heads*vdim]. */
 int sb_mlstm_scan(const float* proj, int n_seqs, const int32_t* seq_row0, const int32_t* seq_slot,
                   int n_heads, int dim, int vdim, const void* i_bias, const void* f_bias, int bias_dtype,
-                  float cap, float q_scale, int max_new, float* state, float* num, float* m_row,
-                  sb_stream_t stream);
+                  float cap, float q_scale, int max_new, float* state, int col_stride, float* num,
+                  float* m_row, sb_stream_t stream);
 int sb_mlstm_out(const float* num, const float* m_row, const float* proj, int n_rows, int n_heads,
                  int dim, int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out,
                  int out_dtype, sb_stream_t stream);

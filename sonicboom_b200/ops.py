@@ -715,17 +715,17 @@ def mlstm_scan(proj: torch.Tensor, plan, n_heads: int, dim: int, vdim: int, i_bi
                f_bias: torch.Tensor, cap: float, q_scale: float, state: torch.Tensor,
                num: torch.Tensor, m_row: torch.Tensor) -> torch.Tensor:
     """Walks every sequence's rows of the step through the recurrence, from and to the state
-    rows of the sequences' slots (float32 [slots, heads, vdim + 1, dim + 1])."""
+    rows of the sequences' slots (float32 [slots, heads, vdim + 1, dim + 1 or more])."""
     rows = proj.shape[0]
     assert proj.dtype == torch.float32 and proj.shape[1] == 2 * n_heads * (dim + vdim + 1)
-    assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (n_heads, vdim + 1, dim + 1)
+    assert state.dtype == torch.float32 and tuple(state.shape[1:3]) == (n_heads, vdim + 1) and state.shape[3] > dim
     assert num.dtype == torch.float32 and tuple(num.shape) == (rows, n_heads, vdim + 1)
     assert m_row.dtype == torch.float32 and tuple(m_row.shape) == (rows, n_heads)
     assert i_bias.dtype == f_bias.dtype and i_bias.numel() == f_bias.numel() == n_heads
     _check(lib().sb_mlstm_scan(_ptr(proj), plan.n_seqs, _i32(plan.seq_row0, "seq_row0"),
                                _i32(plan.seq_slot, "seq_slot"), n_heads, dim, vdim, _ptr(i_bias),
                                _ptr(f_bias), _code(i_bias.dtype), ctypes.c_float(cap),
-                               ctypes.c_float(q_scale), int(plan.max_new), _ptr(state), _ptr(num), _ptr(m_row),
+                               ctypes.c_float(q_scale), int(plan.max_new), _ptr(state), int(state.shape[3]), _ptr(num), _ptr(m_row),
                                _stream()),
            "mlstm_scan")
     return num

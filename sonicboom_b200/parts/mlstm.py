@@ -10,7 +10,7 @@ projected by Wo.
 
 The six input projections are one product over [q | k | v | g | i | f] rows whose float32 result
 feeds the recurrence kernel directly; the state (S with n as one more column, stored column by
-column with a copy of m after each: float32 [heads, vdim + 1, dim + 1]) is fixed-size per-sequence state of the cache
+column with a copy of m after each: float32 [heads, vdim + 1, dim + 1 rounded up to 4]) is fixed-size per-sequence state of the cache
 (`StateNeed`), zeroed when a slot is taken and carried from step to step.
 
 Tensors after the prefix: q, k [heads*dim, width]; v, g [heads*vdim, width]; i, f [heads, width];
@@ -44,7 +44,7 @@ class MLSTM(Mixer):
         self.w_in = self.b_i = self.b_f = self.norm_w = self.w_o = None
 
     def state_need(self):
-        return StateNeed((self.h, self.vd + 1, self.dim + 1), torch.float32)
+        return StateNeed((self.h, self.vd + 1, (self.dim + 4) // 4 * 4), torch.float32)      # columns in 16-byte steps
 
     def tensor_requests(self):
         p, d, h = self.spec.prefix, self.spec.width, self.h
