@@ -3,8 +3,10 @@
 sizes of Qwen2.5-7B with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --arch zolulix [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
 
-Prints ONE JSON line.  A "step" is one decode step of the whole batch.  The default run is a
+Prints ONE JSON line.  (`--arch zolulix` is a measurement of its own: the Zolulix design beside the
+Qwen2.5 decoder of equal sizes and its kernels alone; without it the workload below runs.)  A "step" is one decode step of the whole batch.  The default run is a
 batch of 8 sequences with 2,048-token prompts in a 4,096-token context; decode at batch 1 and
 64 goes into "points".  `value` is timed on the device with CUDA events around K steps of the
 engine's decode loop; `e2e` is the same loop driven through the Python entry point with the
