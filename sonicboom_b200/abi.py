@@ -50,7 +50,14 @@ CORE = {
     "sb_head_linear": ("i", "pizzpiiiiipizzs"),
     "sb_mlstm_scan": ("i", "pippiiippiffipipps"),
     "sb_mlstm_out": ("i", "pppiiiipifpis"),
-    "sb_attention_plain": ("i", "ppiippppipiiiiifs"),
+    "sb_attention_plain": ("i", "ppiippppipiiiiifps"),
+    "sb_stream_add": ("i", "pppiiippifpis"),
+    "sb_polynorm": ("i", "piipifpis"),
+    "sb_attn_prep": ("i", "piiiiiiiiiiiippppifppppipipiis"),
+    "sb_attn_unrotate": ("i", "ppiiiiiipps"),
+    "sb_linrec_prep": ("i", "piiiiiiffiipppfs"),
+    "sb_linrec_scan": ("i", "piiiippippiiipps"),
+    "sb_linrec_out": ("i", "ppiiiiipifpis"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),
     "sb_add_i32": ("i", "piis"),
@@ -63,7 +70,7 @@ ATTENTION = {
     "sb_attention_status": ("i", ""),
     "sb_attention_last_launches": ("i", ""),
     "sb_attention_scratch_bytes": ("z", "iiiii"),
-    "sb_attention": ("i", "ppiiippppipiiiifpzpiiiipzs"),
+    "sb_attention": ("i", "ppiiippppipiiiifpzpiiiipzps"),
     "sb_attention_decode_static": ("i", "ppiiippppipiiiifis"),
     "sb_attention_static_scratch_bytes": ("z", ""),
 }

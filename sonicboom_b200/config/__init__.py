@@ -1,15 +1,17 @@
 """Typed configurations, the model-as-parts records and the architecture registry."""
 from .specs import (ConfigError, DepthMixSpec, FeedForwardSpec, LayerSpec, MixerSpec, ModelSpec,
-                    NormSpec, PositionSpec, ScheduleEntry)
+                    NormSpec, PositionSpec, ScheduleEntry, StreamInjection)
 from .registry import (ARCHITECTURES, Architecture, architecture_name, lookup, read_config_json,
                        register_architecture, spec_from_config_dict)
 from .qwen2 import Qwen2Config
 from .zolulix import ZolulixConfig
+from .mefupel import MefupelConfig
 
 register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, Qwen2Config.to_spec)
 register_architecture("Zolulix", ZolulixConfig.from_dict, ZolulixConfig.to_spec)
+register_architecture("Mefupel", MefupelConfig.from_dict, MefupelConfig.to_spec)
 
-__all__ = ["ConfigError", "DepthMixSpec", "ZolulixConfig", "FeedForwardSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec",
+__all__ = ["ConfigError", "DepthMixSpec", "ZolulixConfig", "MefupelConfig", "StreamInjection", "FeedForwardSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec",
            "PositionSpec", "ScheduleEntry", "ARCHITECTURES", "Architecture", "architecture_name",
            "lookup", "read_config_json", "register_architecture", "spec_from_config_dict",
            "Qwen2Config"]

@@ -98,6 +98,18 @@ class ScheduleEntry:
 
 
 @dataclass(frozen=True)
+class StreamInjection:
+    """Something that joins the stream right before a schedule entry runs: the embedding output
+    once more (`embedding`), and/or row `row` of the tensor `tensor` [rows, width], added to every
+    token's vector."""
+    before_entry: int
+    embedding: bool = False
+    tensor: Optional[str] = None
+    rows: int = 0                  # how many rows the tensor has
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     width: int
@@ -111,6 +123,8 @@ class ModelSpec:
     stop_tokens: tuple = ()
     embedding_scale: float = 1.0        # multiplies every embedding row (1: as stored)
     logit_cap: float = 0.0              # c > 0: logits = c * tanh(logits / c); 0: no cap
+    injections: tuple = ()              # of StreamInjection, at most one per schedule entry
+    unused_tensors: tuple = ()          # (name, shape) of tensors a file may hold that nothing reads
 
     def validate(self) -> None:
         if not self.layers:
@@ -119,6 +133,16 @@ class ModelSpec:
             raise ConfigError(f"embedding_scale {self.embedding_scale} must be positive")
         if self.logit_cap < 0.0:
             raise ConfigError(f"logit_cap {self.logit_cap} must be zero (none) or positive")
+        seen = set()
+        for inj in self.injections:
+            if not 0 <= inj.before_entry < len(self.schedule) or inj.before_entry in seen:
+                raise ConfigError(f"an injection before schedule entry {inj.before_entry}: no such entry, "
+                                  "or it has one already")
+            seen.add(inj.before_entry)
+            if inj.tensor is not None and not 0 <= inj.row < inj.rows:
+                raise ConfigError(f"an injection names row {inj.row} of {inj.tensor}, which has {inj.rows}")
+            if any(l.depth_mix is not None for l in self.layers):
+                raise ConfigError("injections into the stream and depth mixing are not combined")
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule[{i}] names layer {e.layer}, model has {len(self.layers)}")

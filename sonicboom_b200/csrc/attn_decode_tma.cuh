@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(DT_MERGE_THREADS) attn_merge_kernel(const Attn
       wgt[i] = f;
     }
     sum = sb_warp_sum(sum);                        // then a fixed tree over the lanes
-    if (tid == 0) inv_sum = 1.0f / sum;
+    if (tid == 0) inv_sum = 1.0f / (p.sink ? sum + exp2f(p.sink[kvh * G + row % G] * LOG2E - ref) : sum);
   }
   __syncthreads();
   const int c = tid % (HD / 4), group = tid / (HD / 4);
@@ -556,6 +556,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPar
         }
         const size_t out_row = (size_t)(w.row0 + row / G) * p.n_q_heads + w.kvh * G + row % G;
         if (single) {
+          if (p.sink) ll += exp2f(p.sink[w.kvh * G + row % G] * LOG2E - base);
           const float inv = 1.0f / ll;
           uint2 v;
           v.x = pack_bf16(acc.x * inv, acc.y * inv);

@@ -66,6 +66,7 @@ struct AttnParams {
   int n_q_heads, n_kv_heads, window, n_splits;
   int n_seqs;
   float scale_log2;            // scale * log2(e)
+  const float* sink;           // [n_q_heads] or null: exp(sink) joins each row's softmax denominator
   const char* warm;            // decode: bytes the next kernel will read, asked into L2 (or null)
   size_t warm_bytes;
 };
@@ -295,7 +296,9 @@ __global__ void __launch_bounds__(PREFILL_THREADS) attn_prefill_kernel(const Att
   for (int half = 0; half < 2; ++half) {
     const int r = half ? rb : ra;
     if (r >= R) continue;
-    const float inv = 1.0f / l[half];
+    float den = l[half];
+    if (p.sink) den += exp2f(p.sink[kvh * G + r % G] * LOG2E - m[half]);
+    const float inv = 1.0f / den;
     bf16* dst = p.out + ((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD;
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j)
@@ -467,6 +470,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
       fac[w * DEC_ROWS + tid] = f;
       ll += src[HD + 1] * f;
     }
+    // a sink joins the denominator once: here when this block is the row's only split
+    if (p.sink && split_lo == split_hi && tid < R) ll += exp2f(p.sink[kvh * G + tid % G] * LOG2E - base);
     row_m[tid] = mm;
     row_l[tid] = ll;
   }
@@ -543,6 +548,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_kernel(const AttnP
       sum += den[tid * ns + i] * f;
       wgt[tid * ns + i] = f;
     }
+    if (p.sink) sum += exp2f(p.sink[kvh * G + tid % G] * LOG2E - ref);
     den[tid * ns] = 1.0f / sum;
   }
   __syncthreads();
@@ -655,7 +661,8 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
                             const void* cache, int n_q_heads, int n_kv_heads, int hd, int window,
                             float scale, void* scratch, size_t scratch_bytes, int* counters,
                             int n_counters, int max_len, int n_pages, int n_sms,
-                            const void* warm, size_t warm_bytes, cudaStream_t stream) {
+                            const void* warm, size_t warm_bytes, const float* sink,
+                            cudaStream_t stream) {
   if (hd != HD) SB_FAIL(SB_ERR_ARG, "sb_attention: built for head size %d, called with %d", HD, hd);
   if (page_size != KT)
     SB_FAIL(SB_ERR_UNSUPPORTED, "sb_attention: cache pages of %d keys (needs %d)", page_size, KT);
@@ -671,6 +678,7 @@ extern "C" int sb_attention(const void* q, void* out, int n_rows, int n_seqs, in
     SB_FAIL(SB_ERR_ARG, "sb_attention: unaligned operands");
   AttnParams p;
   p.warm = (const char*)warm; p.warm_bytes = sb_warm_bytes(warm, warm_bytes);
+  p.sink = sink;
   p.q = (const bf16*)q; p.out = (bf16*)out;
   p.seq_row0 = seq_row0; p.seq_pos0 = seq_pos0; p.page_off = page_off; p.page_ids = page_ids;
   p.cache = (const bf16*)cache; p.scratch = (float*)scratch; p.counters = counters;
@@ -918,6 +926,7 @@ extern "C" int sb_attention_decode_static(const void* q, void* out, int n_rows, 
   p.counters = g_static_counters_ptr[device];
   p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads; p.window = window; p.n_splits = n_splits;
   p.n_seqs = n_seqs;
+  p.sink = nullptr;
   p.scale_log2 = scale * LOG2E;
   sb_launch<SB_K_ATTENTION>(attn_decode_kernel<DEC_STAGES>, dim3(n_splits, n_kv_heads, n_seqs), dim3(DEC_WARPS * 32), DECODE_SMEM,
             stream, p);

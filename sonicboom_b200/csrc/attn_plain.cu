@@ -5,7 +5,7 @@
 // For the query at absolute position i: key j is visible when j <= i and (window == 0 or
 // i < j + window); s_j = (q . k_j) * scale with the scale applied after the whole dot;
 // out = sum(exp(s_j - m) v_j) / sum(exp(s_j - m)) (core/src/nn/attention.cpp:26-105,
-// 121-183).  Keys are taken in chunks whose boundaries are absolute multiples of the chunk
+// 121-183).  With `sink` (one float32 per query head) the denominator also holds exp(sink_h).  Keys are taken in chunks whose boundaries are absolute multiples of the chunk
 // length and merged in ascending order, as the reference's split decode attention does
 // (core/src/model/emit.cpp:538-544, core/src/nn/cuda_elementwise.cu:886-897), so the sum
 // depends only on the positions, not on the batch or on where the pages lie.
@@ -24,10 +24,10 @@ __global__ void __launch_bounds__(THREADS)
 attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* row_pos,
                   const int32_t* page_off, const int32_t* page_ids, int page_size,
                   const TC* cache, int n_q_heads, int n_kv_heads,
-                  int hd, int window, float scale) {
+                  int hd, int window, float scale, const float* __restrict__ sink) {
   __shared__ float qs[MAX_HD];
   __shared__ float scores[CHUNK];
-  __shared__ float bcast[2];
+  __shared__ float bcast[3];
   sb_pdl_launch();
   sb_pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
@@ -80,6 +80,7 @@ attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* r
       if (lane == 0) {
         bcast[0] = m == -INFINITY ? 0.0f : expf(m - m_new);   // rescale of what came before
         bcast[1] = sum;
+        bcast[2] = m_new;
       }
       m = m_new;
     }
@@ -100,6 +101,13 @@ attn_plain_kernel(const TQ* q, TQ* out, const int32_t* row_seq, const int32_t* r
       }
     }
     __syncthreads();
+  }
+  // a sink adds exp(sink) to the denominator and nothing to the sum
+  if (sink) {
+    const float sk = sink[h], m_run = bcast[2], m_all = fmaxf(m_run, sk), f = expf(m_run - m_all);
+    l = l * f + expf(sk - m_all);
+#pragma unroll
+    for (int i = 0; i < MAX_HD / THREADS; ++i) acc[i] *= f;
   }
   const float inv = 1.0f / l;
 #pragma unroll
@@ -128,7 +136,7 @@ extern "C" int sb_attention_plain(const void* q, void* out, int act_dtype, int n
                                   const int32_t* page_off, const int32_t* page_ids, int page_size,
                                   const void* cache, int cache_dtype, int n_q_heads,
                                   int n_kv_heads, int hd, int window, float scale,
-                                  cudaStream_t stream) {
+                                  const float* sink, cudaStream_t stream) {
   if (int rc = sb_check_attention_args("sb_attention_plain", n_rows, n_q_heads, n_kv_heads, hd,
                                        window, page_size))
     return rc;
@@ -142,7 +150,7 @@ extern "C" int sb_attention_plain(const void* q, void* out, int act_dtype, int n
     SB_DISPATCH_DTYPE(cache_dtype, TC, {
       sb_launch(attn_plain_kernel<TQ, TC>, grid, dim3(THREADS), 0, stream,
           (const TQ*)q, (TQ*)out, row_seq, row_pos, page_off, page_ids, page_size,
-          (const TC*)cache, n_q_heads, n_kv_heads, hd, window, scale);
+          (const TC*)cache, n_q_heads, n_kv_heads, hd, window, scale, sink);
     });
   });
   SB_CHECK_LAUNCH("sb_attention_plain");

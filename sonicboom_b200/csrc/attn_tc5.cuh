@@ -373,7 +373,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_kv, const AttnPa
     if (ok) ok = mbar_wait(tb + 8 * (T5_PFREE + ((n_tiles - 1) & 1)), ((n_tiles - 1) >> 1) & 1, 34);
     if (ok) {
       tc_fence_after();
-      const float inv = 1.0f / l;
+      // a sink adds exp(sink) to the row's denominator (l is relative to m_ref)
+      const float inv = 1.0f / (p.sink ? l + exp2f(p.sink[kvh * G + r % G] * LOG2E - m_ref) : l);
       bf16* dst = p.out + ((size_t)(row0 + r / G) * p.n_q_heads + kvh * G + r % G) * HD;
 #pragma unroll
       for (int c = 0; c < HD / 32; ++c) {

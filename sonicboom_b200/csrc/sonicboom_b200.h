@@ -198,11 +198,62 @@ int sb_mlstm_out(const float* num, const float* m_row, const float* proj, int n_
                  int dim, int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out,
                  int out_dtype, sb_stream_t stream);
 
-/* Plain attention over the paged cache (float32 arithmetic, any head size up to 256). */
+/* Plain attention over the paged cache (float32 arithmetic, any head size up to 1024).  sink: null,
+ * or one float32 per query head whose exponential joins that head's softmax denominator. */
 int sb_attention_plain(const void* q, void* out, int act_dtype, int n_rows, const int32_t* row_seq,
                        const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
                        int page_size, const void* cache, int cache_dtype, int n_q_heads,
-                       int n_kv_heads, int hd, int window, float scale, sb_stream_t stream);
+                       int n_kv_heads, int hd, int window, float scale, const float* sink,
+                       sb_stream_t stream);
+
+/* ---- the stream, the feed-forward and mixers with projections of their own kind ----
+ * out[r] = x[r] + add[r] + vec (add [rows, width] float32 and vec [width] are optional; out may be
+ * x); the optional norm of the finished row as in sb_norm_add. */
+int sb_stream_add(const float* x, const float* add, const void* vec, int vec_dtype, int n_rows,
+                  int width, float* out, const void* next_w, int next_w_dtype, float next_eps,
+                  void* normed, int normed_dtype, sb_stream_t stream);
+/* out[r] = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 with N(u) = u / sqrt(mean(u^2) + eps) over the row's
+ * ff values, powers element by element; coef holds the four numbers. */
+int sb_polynorm(const float* z, int n_rows, int ff, const void* coef, int coef_dtype, float eps,
+                void* out, int out_dtype, sb_stream_t stream);
+/* Projection rows (float32, row stride ld; queries at q_off [n_q_heads x dim], keys at k_off
+ * [n_kv_heads x dim], values at v_off [n_kv_heads x vdim], or v_off < 0: the values are the key
+ * projection as it is) to queries q_out [rows, n_q_heads, hd] and the cache rows of each
+ * position (one entry's pages, heads of size hd >= dim, vdim; the padding is zeros).  With
+ * q_norm / k_norm the whole q (k) projection of a row is RMS-normed with that weight first.  The
+ * first `rot` values of every q and k head turn by float(pos) * inv_freq[i], in pairs
+ * (i, i + rot/2), or (2i, 2i + 1) with `interleaved`; with v_inv_freq [vdim/2] every value head turns
+ * the same way over all vdim.  has_kv = 0: queries only. */
+int sb_attn_prep(const float* proj, int n_rows, int ld, int q_off, int k_off, int v_off,
+                 int n_q_heads, int n_kv_heads, int dim, int vdim, int hd, int rot, int interleaved,
+                 const float* inv_freq, const float* v_inv_freq, const void* q_norm,
+                 const void* k_norm, int norm_dtype, float eps, const int32_t* row_seq,
+                 const int32_t* row_pos, const int32_t* page_off, const int32_t* page_ids,
+                 int page_size, void* cache, int cache_dtype, void* q_out, int q_dtype, int has_kv,
+                 sb_stream_t stream);
+/* out [rows, n_heads * vdim] = the first vdim values of every head of in [rows, n_heads, hd], turned
+ * by -float(pos) * v_inv_freq[i] in the same pairs (v_inv_freq null: copied). */
+int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows, int n_heads, int hd, int vdim,
+                     int interleaved, const float* v_inv_freq, const int32_t* row_pos,
+                     sb_stream_t stream);
+/* In place on projection rows: q (at q_off) and k (at k_off), [n_heads x dim] each, are rotated
+ * (the first `rot` of every head, pairs as in sb_attn_prep) and multiplied by q_scale / k_scale; z
+ * [rows, n_heads * dim], if given, becomes exp(logsigmoid(z) * inv_tau). */
+int sb_linrec_prep(float* proj, int n_rows, int ld, int q_off, int k_off, int n_heads, int dim,
+                   float q_scale, float k_scale, int rot, int interleaved, const float* inv_freq,
+                   const int32_t* row_pos, float* z, float inv_tau, sb_stream_t stream);
+/* S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head and sequence, token by token, from
+ * and to state [slot, n_heads, vdim, dim] float32; a_t from decay [rows, n_heads * dim] or, one
+ * value per head, from head_decay [n_heads] (exactly one of them).  out [rows, n_heads, vdim]. */
+int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
+                   const float* head_decay, int n_seqs, const int32_t* seq_row0,
+                   const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state,
+                   float* out, sb_stream_t stream);
+/* out [rows, n_heads * vdim] = o / sqrt(mean over vdim of o^2 + eps) * norm_w[vdim] (optional) *
+ * silu(g), g at g_off of the projection row. */
+int sb_linrec_out(const float* o, const float* proj, int n_rows, int ld, int g_off, int n_heads,
+                  int vdim, const void* norm_w, int norm_w_dtype, float eps, void* out, int out_dtype,
+                  sb_stream_t stream);
 
 int sb_sample_params_size(void);
 int sb_sample(float* logits, int n_rows, int vocab, const void* params, const int32_t* history,
@@ -221,13 +272,15 @@ int sb_attention_status(void);            /* as sb_tc5_status; -1: no tensor-mem
 int sb_attention_last_launches(void);     /* kernels the last sb_attention call launched */
 size_t sb_attention_scratch_bytes(int n_rows, int n_q_heads, int n_kv_heads, int max_new,
                                   int max_len);
-/* Causal grouped-query attention of a step's rows over one cache entry's pages (bfloat16). */
+/* Causal grouped-query attention of a step's rows over one cache entry's pages (bfloat16).
+ * sink: as in sb_attention_plain. */
 int sb_attention(const void* q, void* out, int n_rows, int n_seqs, int max_new,
                  const int32_t* seq_row0, const int32_t* seq_pos0, const int32_t* page_off,
                  const int32_t* page_ids, int page_size, const void* cache, int n_q_heads,
                  int n_kv_heads, int hd, int window, float scale, void* scratch,
                  size_t scratch_bytes, int* counters, int n_counters, int max_len, int n_pages,
-                 int n_sms, const void* warm, size_t warm_bytes, sb_stream_t stream);
+                 int n_sms, const void* warm, size_t warm_bytes, const float* sink,
+                 sb_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -39,6 +39,9 @@ class DecoderModel:
                     from ..config.specs import ConfigError
                     raise ConfigError(f"schedule[{i}] reads the cache of entry {e.cache_from}, "
                                       f"whose keys and values ({theirs}) are not what it needs ({mine})")
+        # what joins the stream right before a schedule entry: {entry: StreamInjection}
+        self.injections = {inj.before_entry: inj for inj in spec.injections}
+        self.injection_vectors = {}
         self.embedding = self.head = None
 
     # ------------------------------------------------------------------ weights
@@ -50,6 +53,8 @@ class DecoderModel:
             if m is not None:
                 req += m.tensor_requests()
         req += self.final_norm.tensor_requests()
+        req += [TensorRequest(inj.tensor, (inj.rows, s.width), "bias") for inj in s.injections if inj.tensor]
+        req += [TensorRequest(name, tuple(shape), optional=True) for name, shape in s.unused_tensors]
         if s.head_tensor is not None:
             req.append(TensorRequest(s.head_tensor, (s.vocab, s.width)))
         else:
@@ -64,6 +69,12 @@ class DecoderModel:
             if m is not None:
                 m.bind(get)
         self.final_norm.bind(get)
+        tables = {}
+        for e, inj in self.injections.items():
+            if inj.tensor:
+                if inj.tensor not in tables:
+                    tables[inj.tensor] = get(inj.tensor)
+                self.injection_vectors[e] = tables[inj.tensor][inj.row]
         self.head = self.embedding if self.spec.head_tensor is None else get(self.spec.head_tensor)
 
     # ------------------------------------------------------------------ what the cache must hold
@@ -90,7 +101,12 @@ class DecoderModel:
             torch.empty((plan.n_rows, s.width), dtype=torch.float32, device=self.device)
         ops.embed(plan.tokens, self.embedding, x, s.embedding_scale)
         ctx = StepContext(plan=plan, cache=cache)
+        # an injection may add the embedding output again: it is then kept apart from the stream,
+        # which blocks overwrite
+        embedded = x if any(inj.embedding for inj in self.injections.values()) else None
         for i, e in enumerate(s.schedule):
+            if i in self.injections or x is embedded:
+                x = self._inject(self.injections.get(i), i, x, embedded, self.blocks[e.layer], ctx)
             ctx.entry = i
             ctx.owns_cache = e.cache_from is None
             ctx.kv_entry = i if e.cache_from is None else e.cache_from
@@ -98,6 +114,8 @@ class DecoderModel:
             # the next entry's first norm can ride on this entry's last product
             nxt = self.blocks[s.schedule[i + 1].layer] if i + 1 < n else None
             next_norm = nxt.input_norm() if nxt is not None else None
+            if i + 1 in self.injections:
+                next_norm = nxt = None          # the stream changes before the next entry reads it
             ctx.after_block_norm = next_norm if mix is None else None
             # ... and its first weights can be asked into L2 meanwhile, if it would ask late
             ctx.after_block_weights = nxt.first_weights(plan.n_rows) if nxt is not None and mix is None else None
@@ -129,6 +147,22 @@ class DecoderModel:
         ops.linear(hn, self.head, logits)
         return ops.softcap(logits, s.logit_cap) if s.logit_cap > 0.0 else logits
 
+
+    def _inject(self, inj, entry, x, embedded, block, ctx):
+        """x + the embedding output (if asked) + the injection's vector, with the block's first norm
+        written along; without an injection, a copy of the embedding output that the block may
+        overwrite."""
+        out = x if x is not embedded else torch.empty_like(x)
+        norm = block.input_norm()
+        rms = norm.as_rms() if norm is not None else None
+        ride = None
+        if rms is not None:
+            ride = (rms[0], rms[1], torch.empty(x.shape, dtype=self.dtype, device=self.device))
+        ops.stream_add(x, embedded if inj is not None and inj.embedding else None,
+                       self.injection_vectors.get(entry) if inj is not None else None, out, ride)
+        if ride is not None:
+            ctx.keep_normed(norm, out, ride[2])
+        return out
 
     def _one(self):
         if getattr(self, "_one_coef", None) is None:

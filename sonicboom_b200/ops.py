@@ -480,8 +480,10 @@ def attention_lib(head_dim: int):
 
 def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache: torch.Tensor,
               n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
-              kernel: str = "auto", warm: torch.Tensor | None = None) -> torch.Tensor:
+              kernel: str = "auto", warm: torch.Tensor | None = None,
+              sink: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention of the step's rows over one cache entry's pages.
+    `sink` (float32, one per query head): exp(sink) joins that head's softmax denominator.
 
     bfloat16 runs the tensor-core kernels (built for the head size at first use); float32, a
     head size those kernels do not take, or `kernel="plain"` run the plain kernel.  `"mma"` keeps
@@ -492,6 +494,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
     it into L2 while it merges its partial results.  A hint: it changes no result."""
     n = q.shape[0]
     g = plan.groups[group_index]
+    if sink is not None:
+        assert sink.dtype == torch.float32 and sink.numel() == n_q_heads
     al = attention_lib(head_dim) if (q.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16
                                      and kernel != "plain") else None
     if al is not None:
@@ -507,7 +511,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             head_dim, window, ctypes.c_float(scale), _ptr(scratch),
             ctypes.c_size_t(scratch.numel() if scratch is not None else 0),
             _ptr(counters), counters.numel(), plan.max_len, cache.shape[0], _sm_count(q.device),
-            *_warm_args(warm), _stream())
+            *_warm_args(warm), _ptr(sink), _stream())
         if kernel in ("mma", "tma"):
             al.sb_attention_force_mma({"mma": 1, "tma": 2}.get(_os.environ.get("SB_ATTN", ""), 0))
         if rc != 0:
@@ -519,7 +523,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, plan, group_index: int, cache:
             _ptr(q), _ptr(out), _code(q.dtype), n, _i32(plan.row_seq, "row_seq"),
             _i32(plan.row_pos, "row_pos"), _i32(g.page_off, "page_off"),
             _i32(g.page_ids, "page_ids"), g.page_size, _ptr(cache), _code(cache.dtype),
-            n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _stream()),
+            n_q_heads, n_kv_heads, head_dim, window, ctypes.c_float(scale), _ptr(sink), _stream()),
             "attention (plain kernel)")
     return out
 
@@ -740,4 +744,116 @@ def mlstm_out(num: torch.Tensor, m_row: torch.Tensor, proj: torch.Tensor, n_head
     _check(lib().sb_mlstm_out(_ptr(num), _ptr(m_row), _ptr(proj), rows, n_heads, dim, vdim, _ptr(norm_w),
                               _code(norm_w.dtype), ctypes.c_float(eps), _ptr(out), _code(out.dtype),
                               _stream()), "mlstm_out")
+    return out
+
+
+# ---------------------------------------------------------------------- a vector joins the stream
+def stream_add(x: torch.Tensor, add: torch.Tensor | None, vec: torch.Tensor | None, out: torch.Tensor,
+               next_norm: tuple | None = None) -> torch.Tensor:
+    """out = x + add + vec row by row in float32 (`add` [rows, width] and `vec` [width] are optional;
+    out may be x).  `next_norm` = (weight, eps, normed) also writes the RMS norm of the finished rows."""
+    rows, width = x.shape
+    assert x.dtype == out.dtype == torch.float32 and out.shape == x.shape
+    assert add is None or (add.dtype == torch.float32 and add.shape == x.shape)
+    assert vec is None or vec.numel() == width
+    _check(lib().sb_stream_add(_ptr(x), _ptr(add), _ptr(vec), _code(vec.dtype) if vec is not None else 0, rows,
+                               width, _ptr(out), *_next_norm_args(next_norm, width, rows), _stream()),
+           "stream_add")
+    return out
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3 row by row, N(u) = u / sqrt(mean(u^2) + eps);
+    z float32 [rows, ff], coef four numbers."""
+    rows, ff = z.shape
+    assert z.dtype == torch.float32 and tuple(out.shape) == (rows, ff) and coef.numel() == 4
+    _check(lib().sb_polynorm(_ptr(z), rows, ff, _ptr(coef), _code(coef.dtype), ctypes.c_float(eps), _ptr(out),
+                             _code(out.dtype), _stream()), "polynorm")
+    return out
+
+
+# ---------------------------------------------------------------------- attention: rows in and out
+def attn_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_q_heads: int, n_kv_heads: int,
+              dim: int, vdim: int, head_size: int, rotary_dim: int, interleaved: bool,
+              inv_freq: torch.Tensor | None, v_inv_freq: torch.Tensor | None, q_norm: torch.Tensor | None,
+              k_norm: torch.Tensor | None, eps: float, row_seq, row_pos, page_off, page_ids, page_size: int,
+              cache: torch.Tensor | None, q_out: torch.Tensor) -> torch.Tensor:
+    """Projection rows to queries and cache rows (see sb_attn_prep in the kernel library's header):
+    optional RMS norm over the whole q and k projection, rotation in either layout of pairs,
+    values that are the raw keys (`v_off` < 0), values rotated over their whole size (`v_inv_freq`),
+    heads padded with zeros to `head_size`.  `cache=None`: queries only."""
+    n, ld = proj.shape
+    has_kv = cache is not None
+    assert proj.dtype == torch.float32 and tuple(q_out.shape) == (n, n_q_heads, head_size)
+    assert q_off + n_q_heads * dim <= ld and (not has_kv or k_off + n_kv_heads * dim <= ld)
+    assert not has_kv or v_off < 0 or v_off + n_kv_heads * vdim <= ld
+    assert rotary_dim == 0 or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
+    assert v_inv_freq is None or (v_inv_freq.dtype == torch.float32 and v_inv_freq.numel() >= vdim // 2)
+    if q_norm is not None:
+        assert q_norm.dtype == k_norm.dtype and q_norm.numel() == n_q_heads * dim and k_norm.numel() == n_kv_heads * dim
+    _check(lib().sb_attn_prep(
+        _ptr(proj), n, ld, q_off, k_off, v_off, n_q_heads, n_kv_heads, dim, vdim, head_size, rotary_dim,
+        1 if interleaved else 0, _ptr(inv_freq), _ptr(v_inv_freq), _ptr(q_norm), _ptr(k_norm),
+        _code(q_norm.dtype) if q_norm is not None else 0, ctypes.c_float(eps),
+        _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+        _i32(page_off, "page_off") if has_kv else _ptr(None),
+        _i32(page_ids, "page_ids") if has_kv else _ptr(None), page_size, _ptr(cache),
+        _code(cache.dtype) if has_kv else 0, _ptr(q_out), _code(q_out.dtype), 1 if has_kv else 0, _stream()),
+        "attn_prep")
+    return q_out
+
+
+def attn_unrotate(x: torch.Tensor, out: torch.Tensor, n_heads: int, head_size: int, vdim: int,
+                  interleaved: bool, v_inv_freq: torch.Tensor | None, row_pos) -> torch.Tensor:
+    """out [rows, heads * vdim] = the first vdim values of every head of x [rows, heads * head_size],
+    turned back by the row's position when a table is given."""
+    n = out.shape[0]
+    assert x.dtype == out.dtype and x.numel() == n * n_heads * head_size and out.shape[1] == n_heads * vdim
+    _check(lib().sb_attn_unrotate(_ptr(x), _ptr(out), _code(x.dtype), n, n_heads, head_size, vdim,
+                                  1 if interleaved else 0, _ptr(v_inv_freq), _i32(row_pos, "row_pos"), _stream()),
+           "attn_unrotate")
+    return out
+
+
+# ---------------------------------------------------------------------- linear recurrence
+def linrec_prep(proj: torch.Tensor, q_off: int, k_off: int, n_heads: int, dim: int, q_scale: float,
+                k_scale: float, rotary_dim: int, interleaved: bool, inv_freq: torch.Tensor | None, row_pos,
+                z: torch.Tensor | None = None, inv_tau: float = 1.0) -> torch.Tensor:
+    """In place: rotates and scales the q and k of the projection rows; turns decay logits `z`
+    [rows, heads * dim] into decays exp(logsigmoid(z) * inv_tau)."""
+    n, ld = proj.shape
+    assert proj.dtype == torch.float32 and max(q_off, k_off) + n_heads * dim <= ld
+    assert z is None or (z.dtype == torch.float32 and tuple(z.shape) == (n, n_heads * dim))
+    _check(lib().sb_linrec_prep(_ptr(proj), n, ld, q_off, k_off, n_heads, dim, ctypes.c_float(q_scale),
+                                ctypes.c_float(k_scale), rotary_dim, 1 if interleaved else 0, _ptr(inv_freq),
+                                _i32(row_pos, "row_pos"), _ptr(z), ctypes.c_float(inv_tau), _stream()),
+           "linrec_prep")
+    return proj
+
+
+def linrec_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, plan, n_heads: int, dim: int,
+                vdim: int, decay: torch.Tensor | None, head_decay: torch.Tensor | None,
+                state: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Walks every sequence's rows of the step through S = diag(a) S + k v^T, o = S^T q, from and
+    to the state rows of the sequences' slots (float32 [slots, heads, vdim, dim])."""
+    n, ld = proj.shape
+    assert proj.dtype == torch.float32 and state.dtype == torch.float32 and out.dtype == torch.float32
+    assert tuple(state.shape[1:]) == (n_heads, vdim, dim) and tuple(out.shape) == (n, n_heads, vdim)
+    assert decay is None or (decay.dtype == torch.float32 and tuple(decay.shape) == (n, n_heads * dim))
+    assert head_decay is None or (head_decay.dtype == torch.float32 and head_decay.numel() == n_heads)
+    _check(lib().sb_linrec_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(decay), _ptr(head_decay), plan.n_seqs,
+                                _i32(plan.seq_row0, "seq_row0"), _i32(plan.seq_slot, "seq_slot"), n_heads, dim,
+                                vdim, _ptr(state), _ptr(out), _stream()), "linrec_scan")
+    return out
+
+
+def linrec_out(o: torch.Tensor, proj: torch.Tensor, g_off: int, n_heads: int, vdim: int,
+               norm_w: torch.Tensor | None, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out [rows, heads * vdim] = rms(o) per head (optional weight [vdim]) * silu(g of the row)."""
+    n, ld = proj.shape
+    assert tuple(o.shape) == (n, n_heads, vdim) and tuple(out.shape) == (n, n_heads * vdim)
+    assert g_off + n_heads * vdim <= ld and (norm_w is None or norm_w.numel() == vdim)
+    _check(lib().sb_linrec_out(_ptr(o), _ptr(proj), n, ld, g_off, n_heads, vdim, _ptr(norm_w),
+                               _code(norm_w.dtype) if norm_w is not None else 0, ctypes.c_float(eps), _ptr(out),
+                               _code(out.dtype), _stream()), "linrec_out")
     return out

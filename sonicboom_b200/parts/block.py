@@ -144,3 +144,51 @@ class SandwichNormBlock(Block):
         ctx.next_norm = ctx.next_weights = None
         y = self.feed_forward.forward(f, ctx)
         return self._last_join(y, x1, self.feed_forward_post_norm, out, ctx, after, mix)
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Block):
+    """One norm feeds both sublayers: h = norm(x); x <- x + mix(h) + ffn(h) (without a feed-forward,
+    x + mix(h)).  The mixer adds its result to the stream in its last product, the feed-forward
+    adds its own to that, so the sum is ((x + mix) + ffn) in float32; the norm that comes after the
+    block can ride on the last of the two products."""
+
+    def __init__(self, spec, dtype, device):
+        self.dtype = dtype
+        self.mixer_norm = make(NORMS, "norm", spec.mixer_norm, dtype, device)
+        self.mixer = make(MIXERS, "mixer", spec.mixer, dtype, device)
+        self.feed_forward = make(FEED_FORWARDS, "feed-forward", spec.feed_forward, dtype, device) \
+            if spec.feed_forward is not None else None
+        self.parts = [self.mixer_norm, self.mixer] + ([self.feed_forward] if self.feed_forward is not None else [])
+
+    def tensor_requests(self):
+        return [r for p in self.parts for r in p.tensor_requests()]
+
+    def bind(self, get):
+        for p in self.parts:
+            p.bind(get)
+
+    def kv_need(self):
+        return self.mixer.kv_need()
+
+    def state_need(self):
+        return self.mixer.state_need()
+
+    def input_norm(self):
+        return self.mixer_norm
+
+    def first_weights(self, rows):
+        return self.mixer.first_weights(rows)
+
+    def forward(self, x, ctx):
+        after, after_weights = ctx.after_block_norm, ctx.after_block_weights
+        h = ctx.take_normed(self.mixer_norm, x)
+        if h is None:
+            h = self.mixer_norm.forward(x, self.dtype)
+        if self.feed_forward is None:
+            ctx.next_norm, ctx.next_weights = after, after_weights
+            return self.mixer.forward(h, ctx, residual=x)
+        ctx.next_norm = ctx.next_weights = None
+        x = self.mixer.forward(h, ctx, residual=x)
+        ctx.next_norm, ctx.next_weights = after, after_weights
+        return self.feed_forward.forward(h, ctx, residual=x)

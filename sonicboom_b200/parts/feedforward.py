@@ -108,3 +108,43 @@ class ClampedGLU(FeedForward):
         return ctx.linear(t, self.w_down, out,
                           ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
                           residual=residual, act_dtype=self.dtype)
+
+
+@register_feed_forward("polynorm")
+class PolyNormFF(FeedForward):
+    """Feed-forward without a gate whose activation is a cubic in normed powers:
+    y = Wdown (c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3), z = Wup h, powers element by element and
+    N(u) = u / sqrt(mean(u^2) + eps) over a token's intermediate values.  `params`: `eps` and
+    optionally `names`, the tensor names of the two matrices and of the four coefficients after the
+    prefix.  The up product's float32 rows go through `ops.polynorm` (the sums of a row and the
+    activation in float32); the residual add is fused into the down projection."""
+
+    def __init__(self, spec, dtype, device):
+        self.spec, self.dtype = spec, dtype
+        p = dict(spec.params)
+        self.eps = float(p.get("eps", 1e-6))
+        self.names = tuple(p.get("names", ("up", "down", "act")))
+        self.w_up = self.w_down = self.coef = None
+
+    def tensor_requests(self):
+        p, d, ff = self.spec.prefix, self.spec.width, self.spec.intermediate
+        up, down, act = self.names
+        return [TensorRequest(p + up, (ff, d)), TensorRequest(p + down, (d, ff)),
+                TensorRequest(p + act, (4,), "bias")]
+
+    def bind(self, get):
+        p = self.spec.prefix
+        up, down, act = self.names
+        self.w_up, self.w_down, self.coef = get(p + up), get(p + down), get(p + act)
+
+    def forward(self, h, ctx, residual=None):
+        rows, ff = h.shape[0], self.spec.intermediate
+        z = torch.empty((rows, ff), dtype=torch.float32, device=h.device)
+        ops.linear(h, self.w_up, z)
+        t = torch.empty((rows, ff), dtype=self.dtype, device=h.device)
+        ops.polynorm(z, self.coef, self.eps, t)
+        out = residual if residual is not None else \
+            torch.empty((rows, self.spec.width), dtype=torch.float32, device=h.device)
+        return ctx.linear(t, self.w_down, out,
+                          ops.EPI_RESIDUAL if residual is not None else ops.EPI_NONE,
+                          residual=residual, act_dtype=self.dtype)

@@ -42,3 +42,16 @@ class ScalarRMSNorm(RMSNorm):
 
     def bind(self, get):
         self.weight = get(self.tensor).reshape(1).expand(self.width).contiguous()
+
+
+@register_norm("rmsnorm_one_plus")
+class OnePlusRMSNorm(RMSNorm):
+    """RMS norm whose stored weight is an offset from one: y = x / sqrt(mean(x^2) + eps) * (1 + w).
+    Bound, 1 + w is worked out once in float32 (a bfloat16 sum would lose the offset's low bits),
+    so every kernel that takes an RMS norm's weight vector serves it unchanged."""
+
+    def tensor_requests(self):
+        return [TensorRequest(self.tensor, (self.width,), "bias")]
+
+    def bind(self, get):
+        self.weight = (get(self.tensor).float() + 1.0).contiguous()

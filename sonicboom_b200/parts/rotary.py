@@ -57,3 +57,29 @@ class RotaryInterleaved(PositionEncoding):
         i = np.arange(max(1, self.rotary_dim // 2), dtype=np.float64)
         inv = np.power(np.float64(spec.theta), -2.0 * i / np.float64(self.rotary_dim))
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
+
+
+def frequency_table(base: float, n: int, device) -> torch.Tensor:
+    """float32 [max(1, n/2)]: base^(-2i/n), worked out in double precision and rounded once."""
+    i = np.arange(max(1, n // 2), dtype=np.float64)
+    inv = np.power(np.float64(base), -2.0 * i / np.float64(max(n, 1)))
+    return torch.from_numpy(inv.astype(np.float32)).to(device)
+
+
+@register_position_encoding("rope_halves")
+class RotaryHalves(PositionEncoding):
+    """Rotation of pairs half a prefix apart: elements i and i + rotary_dim/2 turn by
+    position * base^(-2i / rotary_dim), i < rotary_dim / 2; elements from rotary_dim on pass
+    unchanged (rotary_dim 0: nothing turns).  The pairs are "rope_neox"'s; the table is worked out in double precision
+    and rounded once, as "rope_interleaved"'s is, and the kernels that take a `layout`
+    (`ops.attn_prep`, `ops.linrec_prep`) serve both."""
+    layout = "halves"
+
+    def __init__(self, spec, dtype, device):
+        self.head_dim = spec.head_dim
+        self.rotary_dim = spec.rotary_dim
+        if self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
+            from ..config.specs import ConfigError
+            raise ConfigError(f"rotary_dim {self.rotary_dim} must be even and at most the rotated "
+                              f"vector's length {self.head_dim}")
+        self.inv_freq = frequency_table(spec.theta, self.rotary_dim, device)

@@ -16,7 +16,7 @@ import torch
 @dataclass(frozen=True)
 class TensorRequest:
     name: str
-    shape: tuple
+    shape: tuple                # -1: any size there
     role: str = "matrix"        # matrix | embedding | bias | norm | table (integers)
     optional: bool = False      # absent is fine, present is not "unexpected"
 
@@ -38,6 +38,13 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _shape_fits(have, want) -> bool:
+    """Whether a stored shape is the requested one; -1 in a request stands for any size (a size
+    that only the stored tensor knows)."""
+    have, want = tuple(have), tuple(want)
+    return len(have) == len(want) and all(w == -1 or h == w for h, w in zip(have, want))
+
+
 def check(source, requests) -> None:
     """Raises WeightError unless `source` holds exactly the requested tensors."""
     wanted = {}
@@ -53,7 +60,7 @@ def check(source, requests) -> None:
                 missing.append((name, r.shape))
             continue
         dtype, shape = source.info(name)
-        if tuple(shape) != tuple(r.shape):
+        if not _shape_fits(shape, r.shape):
             wrong_shape.append((name, r.shape, shape))
         if r.role == "table":
             if dtype.is_floating_point:

@@ -106,6 +106,10 @@ class RandomSource:
     def __init__(self, requests, seed: int, std=0.02, bias_std=None, norm_std=0.0,
                  dtype=torch.bfloat16, device="cpu"):
         self.requests = {r.name: r for r in requests if not r.optional}
+        open_sizes = [r.name for r in self.requests.values() if -1 in tuple(r.shape)]
+        if open_sizes:
+            raise ValueError(f"random weights need every size: the configuration leaves a size of "
+                             f"{', '.join(open_sizes)} to the stored tensor")
         self.seed, self.std = int(seed), float(std)
         self.bias_std = float(std if bias_std is None else bias_std)
         self.norm_std = float(norm_std)
