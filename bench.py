@@ -4,6 +4,7 @@ sizes of Qwen2.5-7B with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --arch zolulix [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
+    python bench.py --arch mefupel [--sizes w2048,w3584] [--prompt 2048] [--batch 8] [--steps K]
 
 Prints ONE JSON line.  (`--arch zolulix` is a measurement of its own: the Zolulix design beside the
 Qwen2.5 decoder of equal sizes and its kernels alone; without it the workload below runs.)  A "step" is one decode step of the whole batch.  The default run is a
@@ -430,27 +431,25 @@ ZOLULIX_SIZES = {
 }
 
 
-def run_zolulix(args) -> int:
-    """Prefill and decode throughput of Zolulix models at layer sizes of real models (random
-    weights), beside the Qwen2.5 decoder of equal width, depth, feed-forward and vocabulary; and
-    each new kernel alone with the bytes it must move, beside the like kernel of that decoder."""
-    import torch
-    import sonicboom_b200 as sb
-    from sonicboom_b200 import ops
-    from sonicboom_b200.engine.decode import DecodeLoop
+class ArchBench:
+    """What the per-architecture measurements share: a timer over single calls with L2 flushed,
+    and the prefill and decode points of one model."""
 
-    torch.cuda.set_device(0)
-    dev, pk = "cuda:0", peaks()
-    gen = torch.Generator().manual_seed(1)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)      # larger than L2
+    def __init__(self):
+        import torch
+        torch.cuda.set_device(0)
+        self.dev, self.pk = "cuda:0", peaks()
+        self.gen = torch.Generator().manual_seed(1)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)      # larger than L2
 
-    def timed(fn, reps=5):
+    def timed(self, fn, reps=5):
         """Median device time (ms) of fn(), L2 flushed before every timed call, after 3 warm-up calls."""
+        import torch
         for _ in range(3):
             fn()
         ts = []
         for _ in range(reps):
-            flush.zero_()
+            self.flush.zero_()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -459,7 +458,11 @@ def run_zolulix(args) -> int:
             ts.append(a.elapsed_time(b))
         return sorted(ts)[len(ts) // 2]
 
-    def model_points(m, n_prompt, batch, steps, warmup):
+    def model_points(self, m, n_prompt, batch, steps, warmup):
+        import torch
+        import sonicboom_b200 as sb
+        from sonicboom_b200.engine.decode import DecodeLoop
+        gen, timed = self.gen, self.timed
         vocab = m.spec.vocab
         engine = sb.Engine(m, max_tokens=max(n_prompt, batch * (n_prompt + warmup + 2 * steps + 64)), n_slots=batch)
         p = torch.randint(0, vocab, (n_prompt,), generator=gen).tolist()
@@ -494,81 +497,103 @@ def run_zolulix(args) -> int:
                 "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch / (ms / 1e3), 1),
                 "decode_launches_per_step": launches, "weight_bytes": weight_bytes(m)}
 
+
+
+def zolulix_kernels(bench, z, rows):
+    """Each new kernel alone at `rows` rows with its algorithmic bytes (what it must read and
+    write once), and the decoder's like kernels (norm, rotation + cache write)."""
+    import torch
+    from sonicboom_b200 import ops
+    dev, pk, timed = bench.dev, bench.pk, bench.timed
+    W, ff = z["width"], z["ff"]
+    f32, bf = torch.float32, torch.bfloat16
+    out = {}
+
+    def rec(name, ms, nbytes, flops=0):
+        out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
+                     "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+        if flops:
+            out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+    x, y = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+    w = torch.ones(W, device=dev, dtype=bf)
+    o, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
+    rec("rmsnorm (decoder's)", timed(lambda: ops.rmsnorm(x, w, 1e-5, nb)), rows * W * 6)
+    rec("norm_add + next norm", timed(lambda: ops.norm_add(y, x, w, 1e-5, o, (w, 1e-5, nb))), rows * W * 14)
+    n_in = z["n_layers"] // 2 + 1
+    planes = torch.randn(n_in, rows, W, device=dev)
+    coef = torch.ones(n_in, device=dev, dtype=bf)
+    rec(f"depth_mix of {n_in} + next norm", timed(lambda: ops.depth_mix(planes, n_in, coef, o, (w, 1e-5, nb))),
+        rows * W * (4 * n_in + 6))
+    gu, t = torch.randn(rows, 2 * ff, device=dev), torch.empty(rows, ff, device=dev, dtype=bf)
+    rec("glu_clamped", timed(lambda: ops.glu_clamped(gu, 7.0, 1.702, t)), rows * ff * 10)
+    H, dim, rd, vd, rank = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["rank"]
+    wide = rank + rd
+    proj = torch.randn(rows, H * (dim + rd) + wide, device=dev)
+    cache = torch.zeros((rows + 63) // 64, 2, 1, 64, wide, device=dev, dtype=bf)
+    q_wide = torch.empty(1, rows, H, wide, device=dev, dtype=bf)
+    inv = torch.ones(rd // 2, device=dev)
+    row_seq = torch.zeros(rows, dtype=torch.int32, device=dev)
+    row_pos = torch.arange(rows, dtype=torch.int32, device=dev)
+    page_off = torch.tensor([0, cache.shape[0]], dtype=torch.int32, device=dev)
+    page_ids = torch.arange(cache.shape[0], dtype=torch.int32, device=dev)
+    cn = torch.ones(rank, device=dev, dtype=bf)
+    rec("latent_prep", timed(lambda: ops.latent_prep(proj, H, dim, rd, rank, rd, inv, row_seq, row_pos, page_off,
+                                                     page_ids, 64, cn, 1e-5, cache, q_wide)),
+        rows * (4 * (H * rd + wide) + 2 * H * rd + 4 * wide))
+    hq, hkv, hd = 28, 4, 128
+    qkv = torch.randn(rows, (hq + 2 * hkv) * hd, device=dev)
+    cache2 = torch.zeros((rows + 63) // 64, 2, hkv, 64, hd, device=dev, dtype=bf)
+    q2 = torch.empty(rows, hq, hd, device=dev, dtype=bf)
+    inv2 = torch.ones(hd // 2, device=dev)
+    rec("rope_store (decoder's)", timed(lambda: ops.rope_store(qkv, hq, hkv, hd, hd, inv2, row_seq, row_pos, page_off,
+                                                                page_ids, 64, cache2, q2)),
+        rows * (hq + 2 * hkv) * hd * 6)
+    ukt = torch.randn(H, rank, dim, device=dev).to(bf)
+    uv = torch.randn(H, vd, rank, device=dev).to(bf)
+    zz = torch.randn(rows, H * wide, device=dev).to(bf)
+    mixed = torch.empty(rows, H * vd, device=dev, dtype=bf)
+    rec("head_linear (queries to latent)",
+        timed(lambda: ops.head_linear(proj, 0, proj.shape[1], dim + rd, ukt, q_wide, 0, H * wide, wide, rows)),
+        rows * H * (4 * dim + 2 * rank) + 2 * H * rank * dim, 2 * rows * H * dim * rank)
+    rec("head_linear (latent to values)",
+        timed(lambda: ops.head_linear(zz, 0, H * wide, wide, uv, mixed, 0, H * vd, vd, rows)),
+        rows * H * (2 * rank + 2 * vd) + 2 * H * rank * vd, 2 * rows * H * vd * rank)
+    rh, rdim, rvd = z["r_heads"], z["r_dim"], z["r_vdim"]
+
+    class Plan:
+        n_seqs = 1 if rows > 64 else rows
+    per = Plan.max_new = rows // Plan.n_seqs
+    Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
+    Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
+    rproj = torch.randn(rows, 2 * rh * (rdim + rvd + 1), device=dev) * 0.1
+    state = torch.zeros(Plan.n_seqs, rh, rvd + 1, (rdim + 4) // 4 * 4, device=dev)
+    num, m_row = torch.empty(rows, rh, rvd + 1, device=dev), torch.empty(rows, rh, device=dev)
+    bi = torch.zeros(rh, device=dev, dtype=bf)
+    rec(f"mlstm_scan ({Plan.n_seqs} sequence(s) of {per})",
+        timed(lambda: ops.mlstm_scan(rproj, Plan, rh, rdim, rvd, bi, bi, 15.0, rdim ** -0.5, state, num, m_row)),
+        rows * rh * 4 * (2 * rdim + 2 * rvd + 3) + 8 * state.numel(), 4 * rows * rh * rdim * (rvd + 1))
+    ro = torch.empty(rows, rh * rvd, device=dev, dtype=bf)
+    nw = torch.ones(rh * rvd, device=dev, dtype=bf)
+    rec("mlstm_out", timed(lambda: ops.mlstm_out(num, m_row, rproj, rh, rdim, rvd, nw, 1e-5, ro)),
+        rows * rh * rvd * 10)
+    return out
+
+
+
+def run_zolulix(args) -> int:
+    """Prefill and decode throughput of Zolulix models at layer sizes of real models (random
+    weights), beside the Qwen2.5 decoder of equal width, depth, feed-forward and vocabulary; and
+    each new kernel alone with the bytes it must move, beside the like kernel of that decoder."""
+    import torch
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+
+    bench = ArchBench()
+    dev, pk = bench.dev, bench.pk
+    model_points = bench.model_points
+
     def kernels(z, rows):
-        """Each new kernel alone at `rows` rows with its algorithmic bytes (what it must read and
-        write once), and the decoder's like kernels (norm, rotation + cache write)."""
-        W, ff = z["width"], z["ff"]
-        f32, bf = torch.float32, torch.bfloat16
-        out = {}
-
-        def rec(name, ms, nbytes, flops=0):
-            out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
-                         "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
-            if flops:
-                out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
-        x, y = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
-        w = torch.ones(W, device=dev, dtype=bf)
-        o, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
-        rec("rmsnorm (decoder's)", timed(lambda: ops.rmsnorm(x, w, 1e-5, nb)), rows * W * 6)
-        rec("norm_add + next norm", timed(lambda: ops.norm_add(y, x, w, 1e-5, o, (w, 1e-5, nb))), rows * W * 14)
-        n_in = z["n_layers"] // 2 + 1
-        planes = torch.randn(n_in, rows, W, device=dev)
-        coef = torch.ones(n_in, device=dev, dtype=bf)
-        rec(f"depth_mix of {n_in} + next norm", timed(lambda: ops.depth_mix(planes, n_in, coef, o, (w, 1e-5, nb))),
-            rows * W * (4 * n_in + 6))
-        gu, t = torch.randn(rows, 2 * ff, device=dev), torch.empty(rows, ff, device=dev, dtype=bf)
-        rec("glu_clamped", timed(lambda: ops.glu_clamped(gu, 7.0, 1.702, t)), rows * ff * 10)
-        H, dim, rd, vd, rank = z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["rank"]
-        wide = rank + rd
-        proj = torch.randn(rows, H * (dim + rd) + wide, device=dev)
-        cache = torch.zeros((rows + 63) // 64, 2, 1, 64, wide, device=dev, dtype=bf)
-        q_wide = torch.empty(1, rows, H, wide, device=dev, dtype=bf)
-        inv = torch.ones(rd // 2, device=dev)
-        row_seq = torch.zeros(rows, dtype=torch.int32, device=dev)
-        row_pos = torch.arange(rows, dtype=torch.int32, device=dev)
-        page_off = torch.tensor([0, cache.shape[0]], dtype=torch.int32, device=dev)
-        page_ids = torch.arange(cache.shape[0], dtype=torch.int32, device=dev)
-        cn = torch.ones(rank, device=dev, dtype=bf)
-        rec("latent_prep", timed(lambda: ops.latent_prep(proj, H, dim, rd, rank, rd, inv, row_seq, row_pos, page_off,
-                                                         page_ids, 64, cn, 1e-5, cache, q_wide)),
-            rows * (4 * (H * rd + wide) + 2 * H * rd + 4 * wide))
-        hq, hkv, hd = 28, 4, 128
-        qkv = torch.randn(rows, (hq + 2 * hkv) * hd, device=dev)
-        cache2 = torch.zeros((rows + 63) // 64, 2, hkv, 64, hd, device=dev, dtype=bf)
-        q2 = torch.empty(rows, hq, hd, device=dev, dtype=bf)
-        inv2 = torch.ones(hd // 2, device=dev)
-        rec("rope_store (decoder's)", timed(lambda: ops.rope_store(qkv, hq, hkv, hd, hd, inv2, row_seq, row_pos, page_off,
-                                                                    page_ids, 64, cache2, q2)),
-            rows * (hq + 2 * hkv) * hd * 6)
-        ukt = torch.randn(H, rank, dim, device=dev).to(bf)
-        uv = torch.randn(H, vd, rank, device=dev).to(bf)
-        zz = torch.randn(rows, H * wide, device=dev).to(bf)
-        mixed = torch.empty(rows, H * vd, device=dev, dtype=bf)
-        rec("head_linear (queries to latent)",
-            timed(lambda: ops.head_linear(proj, 0, proj.shape[1], dim + rd, ukt, q_wide, 0, H * wide, wide, rows)),
-            rows * H * (4 * dim + 2 * rank) + 2 * H * rank * dim, 2 * rows * H * dim * rank)
-        rec("head_linear (latent to values)",
-            timed(lambda: ops.head_linear(zz, 0, H * wide, wide, uv, mixed, 0, H * vd, vd, rows)),
-            rows * H * (2 * rank + 2 * vd) + 2 * H * rank * vd, 2 * rows * H * vd * rank)
-        rh, rdim, rvd = z["r_heads"], z["r_dim"], z["r_vdim"]
-
-        class Plan:
-            n_seqs = 1 if rows > 64 else rows
-        per = Plan.max_new = rows // Plan.n_seqs
-        Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
-        Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
-        rproj = torch.randn(rows, 2 * rh * (rdim + rvd + 1), device=dev) * 0.1
-        state = torch.zeros(Plan.n_seqs, rh, rvd + 1, (rdim + 4) // 4 * 4, device=dev)
-        num, m_row = torch.empty(rows, rh, rvd + 1, device=dev), torch.empty(rows, rh, device=dev)
-        bi = torch.zeros(rh, device=dev, dtype=bf)
-        rec(f"mlstm_scan ({Plan.n_seqs} sequence(s) of {per})",
-            timed(lambda: ops.mlstm_scan(rproj, Plan, rh, rdim, rvd, bi, bi, 15.0, rdim ** -0.5, state, num, m_row)),
-            rows * rh * 4 * (2 * rdim + 2 * rvd + 3) + 8 * state.numel(), 4 * rows * rh * rdim * (rvd + 1))
-        ro = torch.empty(rows, rh * rvd, device=dev, dtype=bf)
-        nw = torch.ones(rh * rvd, device=dev, dtype=bf)
-        rec("mlstm_out", timed(lambda: ops.mlstm_out(num, m_row, rproj, rh, rdim, rvd, nw, 1e-5, ro)),
-            rows * rh * rvd * 10)
-        return out
+        return zolulix_kernels(bench, z, rows)
 
     result = {"arch": "zolulix", "impl": "ours", "dtype": "bf16", "peaks": pk, "sizes": {},
               "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
@@ -587,6 +612,147 @@ def run_zolulix(args) -> int:
                 torch.cuda.empty_cache()
             rec["kernels_prefill_rows_%d" % args.prompt] = kernels(z, args.prompt)
             rec["kernels_decode_rows_%d" % args.batch] = kernels(z, args.batch)
+            result["sizes"][name] = rec
+    ops.check_status()
+    result["clocks"] = clocks.summary()
+    print(json.dumps(result))
+    return 0
+
+
+# ---------------------------------------------------------------------------- --arch mefupel
+def mefupel_config(width, n_layers, ff, vocab, heads, kv_heads, dim, window, r_heads, r_dim, r_vdim, rank=16):
+    """A Mefupel model of the given layer sizes: attention, attention, gated linear attention and
+    the side-by-side layer in turn, every layer with its feed-forward; no loop (the weights are then
+    what a step reads, as in the model beside it)."""
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "mask": {"size": window}, "rot": {"base": 250000.0, "dims": dim}}
+    left = dict(att, rot={"base": 10000.0, "dims": dim // 2})
+    right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"base": 1e6, "dims": r_dim},
+             "decay": [1.0 - 2.0 ** -(5 + i % 8) for i in range(r_heads)]}
+    kinds = [("attention", att), ("attention", att),
+             ("gla", {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 16.0, "decay_rank": rank}),
+             ("parallel", {"left": left, "right": right})]
+    layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": ff}}
+              for i in range(n_layers)]
+    return {"architecture": "Mefupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+MEFUPEL_SIZES = {
+    # name: Mefupel sizes; the Zolulix and Qwen2.5 models beside it are ZOLULIX_SIZES[name]
+    "w2048": dict(width=2048, n_layers=8, ff=8192, vocab=32768, heads=16, kv_heads=4, dim=128, window=1024,
+                  r_heads=8, r_dim=128, r_vdim=256),
+    "w3584": dict(width=3584, n_layers=8, ff=18944, vocab=32768, heads=28, kv_heads=4, dim=128, window=4096,
+                  r_heads=14, r_dim=128, r_vdim=256),
+}
+
+
+def mefupel_kernels(bench, z, rows):
+    """Each kernel that came with Mefupel alone at `rows` rows, with the bytes it must read and
+    write once."""
+    import torch
+    from sonicboom_b200 import ops
+    dev, pk, timed = bench.dev, bench.pk, bench.timed
+    W, ff = z["width"], z["ff"]
+    f32, bf = torch.float32, torch.bfloat16
+    out = {}
+
+    def rec(name, ms, nbytes, flops=0):
+        out[name] = {"us": round(ms * 1e3, 2), "bytes": int(nbytes),
+                     "hbm_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 3)}
+        if flops:
+            out[name]["tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+    x, e = torch.randn(rows, W, device=dev), torch.randn(rows, W, device=dev)
+    vec = torch.ones(W, device=dev, dtype=bf)
+    w = torch.ones(W, device=dev)
+    o, nb = torch.empty(rows, W, device=dev), torch.empty(rows, W, device=dev, dtype=bf)
+    rec("stream_add + next norm", timed(lambda: ops.stream_add(x, e, vec, o, (w, 1e-6, nb))), rows * W * 14)
+    zf, t = torch.randn(rows, ff, device=dev), torch.empty(rows, ff, device=dev, dtype=bf)
+    coef = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev, dtype=bf)
+    rec("polynorm", timed(lambda: ops.polynorm(zf, coef, 1e-6, t)), rows * ff * 6)
+    H, G, d = z["heads"], z["kv_heads"], z["dim"]
+    n_pages = (rows + 63) // 64
+    row_seq = torch.zeros(rows, dtype=torch.int32, device=dev)
+    row_pos = torch.arange(rows, dtype=torch.int32, device=dev)
+    page_off = torch.tensor([0, n_pages], dtype=torch.int32, device=dev)
+    page_ids = torch.arange(n_pages, dtype=torch.int32, device=dev)
+    cache = torch.zeros(n_pages, 2, G, 64, d, device=dev, dtype=bf)
+    q = torch.empty(rows, H, d, device=dev, dtype=bf)
+    inv = torch.ones(d // 2, device=dev)
+    proj = torch.randn(rows, (H + 2 * G) * d, device=dev)
+    rec("attn_prep (rotated values)",
+        timed(lambda: ops.attn_prep(proj, 0, H * d, (H + G) * d, H, G, d, d, d, d, True, inv, inv, None, None, 1e-6,
+                                    row_seq, row_pos, page_off, page_ids, 64, cache, q)),
+        rows * (H + 2 * G) * d * 6)
+    proj2 = torch.randn(rows, (H + G) * d, device=dev)
+    qn, kn = torch.ones(H * d, device=dev, dtype=bf), torch.ones(G * d, device=dev, dtype=bf)
+    rec("attn_prep (norms, keys as values)",
+        timed(lambda: ops.attn_prep(proj2, 0, H * d, -1, H, G, d, d, d, d // 2, False, inv, None, qn, kn, 1e-6,
+                                    row_seq, row_pos, page_off, page_ids, 64, cache, q)),
+        rows * ((H + G) * d * 4 + (H + 2 * G) * d * 2))
+    att, back = torch.randn(rows, H * d, device=dev).to(bf), torch.empty(rows, H * d, device=dev, dtype=bf)
+    rec("attn_unrotate", timed(lambda: ops.attn_unrotate(att, back, H, d, d, True, inv, row_pos)), rows * H * d * 4)
+    rh, rd, rv = z["r_heads"], z["r_dim"], z["r_vdim"]
+
+    class Plan:
+        n_seqs = 1 if rows > 64 else rows
+    per = rows // Plan.n_seqs
+    Plan.seq_row0 = torch.arange(0, rows + 1, per, dtype=torch.int32, device=dev)
+    Plan.seq_slot = torch.arange(Plan.n_seqs, dtype=torch.int32, device=dev)
+    rproj = torch.randn(rows, 2 * rh * (rd + rv), device=dev) * 0.1
+    zl = torch.randn(rows, rh * rd, device=dev)
+    rinv = torch.ones(rd // 2, device=dev)
+    rec("linrec_prep (decay logits)", timed(lambda: ops.linrec_prep(rproj, 0, rh * rd, rh, rd, rd ** -0.5, 1.0, 0, False,
+                                                                    None, row_pos, zl, 1.0 / 16.0)),
+        rows * rh * rd * 24)
+    rec("linrec_prep (rotation)", timed(lambda: ops.linrec_prep(rproj, 0, rh * rd, rh, rd, 1.0, rd ** -0.5, rd, False,
+                                                                rinv, row_pos)), rows * rh * rd * 16)
+    decay = torch.rand(rows, rh * rd, device=dev) * 0.1 + 0.9
+    state = torch.zeros(Plan.n_seqs, rh, rv, rd, device=dev)
+    ro = torch.empty(rows, rh, rv, device=dev)
+    scan_bytes = rows * rh * 4 * (3 * rd + 2 * rv) + 8 * state.numel()
+    rec(f"linrec_scan, a decay per channel ({Plan.n_seqs} sequence(s) of {per})",
+        timed(lambda: ops.linrec_scan(rproj, 0, rh * rd, 2 * rh * rd, Plan, rh, rd, rv, decay, None, state, ro)),
+        scan_bytes, 4 * rows * rh * rd * rv)
+    hdec = torch.full((rh,), 0.99, device=dev)
+    rec(f"linrec_scan, a decay per head ({Plan.n_seqs} sequence(s) of {per})",
+        timed(lambda: ops.linrec_scan(rproj, 0, rh * rd, 2 * rh * rd, Plan, rh, rd, rv, None, hdec, state, ro)),
+        scan_bytes - rows * rh * rd * 4, 4 * rows * rh * rd * rv)
+    mixed = torch.empty(rows, rh * rv, device=dev, dtype=bf)
+    nw = torch.ones(rv, device=dev, dtype=bf)
+    rec("linrec_out", timed(lambda: ops.linrec_out(ro, rproj, 2 * rh * rd + rh * rv, rh, rv, nw, 1e-6, mixed)),
+        rows * rh * rv * 10)
+    return out
+
+
+def run_mefupel(args) -> int:
+    """Prefill and decode throughput of Mefupel models at layer sizes of real models (random
+    weights) beside the Zolulix and Qwen2.5 models of equal width, depth, feed-forward and
+    vocabulary; and each of its kernels alone beside the like kernels of those models."""
+    import torch
+    import sonicboom_b200 as sb
+    from sonicboom_b200 import ops
+
+    bench = ArchBench()
+    dev = bench.dev
+    result = {"arch": "mefupel", "impl": "ours", "dtype": "bf16", "peaks": bench.pk, "sizes": {},
+              "data": "synthetic: random N(0,0.02) weights, uniform random token ids",
+              "timing": "CUDA events; kernels alone: median of 5 after 3 warm-up calls, L2 flushed "
+                        "(256 MB written) before each; models: prefill median of 3, decode one region of K steps"}
+    with ClockSampler() as clocks:
+        for name, z in MEFUPEL_SIZES.items():
+            if args.sizes and name not in args.sizes.split(","):
+                continue
+            zz, q = ZOLULIX_SIZES[name]
+            rec = {"mefupel_config": dict(z)}
+            for label, cfg in (("mefupel", mefupel_config(**z)), ("zolulix (equal width, layers, ff, vocab)", zolulix_config(**zz)),
+                               ("qwen2.5 (equal width, layers, ff, vocab)", q)):
+                m = sb.random_model(cfg, seed=0, dtype="bfloat16", device=dev, std=0.02)
+                rec[label] = bench.model_points(m, args.prompt, args.batch, args.steps, args.warmup)
+                del m
+                torch.cuda.empty_cache()
+            for rows in (args.prompt, args.batch):
+                rec["kernels_rows_%d" % rows] = mefupel_kernels(bench, z, rows)
+                rec["like_kernels_rows_%d" % rows] = zolulix_kernels(bench, zz, rows)
             result["sizes"][name] = rec
     ops.check_status()
     result["clocks"] = clocks.summary()
@@ -613,12 +779,13 @@ def main() -> int:
                     help="run one phase only and print a short line (small cases for profilers)")
     ap.add_argument("--eager", action="store_true",
                     help="with --only decode: launch the step kernel by kernel, not as a graph")
-    ap.add_argument("--arch", choices=["qwen2", "zolulix"], default="qwen2",
+    ap.add_argument("--arch", choices=["qwen2", "zolulix", "mefupel"], default="qwen2",
                     help="zolulix: that design's prefill and decode throughput and its kernels alone, "
                          "beside the Qwen2.5 decoder of equal sizes (its own JSON line; the default "
-                         "workload is unchanged)")
-    ap.add_argument("--sizes", default="", help="with --arch zolulix: which of its sizes to run (comma separated)")
-    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix: prompt length")
+                         "workload is unchanged); mefupel: the same for that design, beside Zolulix and "
+                         "Qwen2.5 models of equal sizes")
+    ap.add_argument("--sizes", default="", help="with --arch zolulix / mefupel: which of its sizes to run (comma separated)")
+    ap.add_argument("--prompt", type=int, default=2048, help="with --arch zolulix / mefupel: prompt length")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -629,6 +796,8 @@ def main() -> int:
         args.warmup = 3
     if args.arch == "zolulix":
         return run_zolulix(args)
+    if args.arch == "mefupel":
+        return run_mefupel(args)
     return run(args)
 
 
