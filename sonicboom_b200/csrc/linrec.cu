@@ -9,82 +9,245 @@
 //
 // A column of S (the `dim` values that belong to one value channel) is shared by 16 lanes that
 // keep their runs of it in registers for the whole step; a warp holds two columns, a block
-// eight.  Per token a lane multiplies and adds its run, and the lanes' partial dot products
-// with q are added by four exchanges.  The next token's q, k, decay and v are requested before
-// the running token is computed.  State: float32 [slot, heads, vdim, dim] (column by column).
+// eight.  Tokens come in groups of 16: a group's q, k, decays and the block's values are staged in
+// shared memory with cp.async one or two groups ahead of the one that is computed; per token a
+// lane multiplies and adds its runs, and the 16 lanes' partial dot products of the group's 16
+// tokens are added in 15 exchanges, after which lane i holds token i's sum (the same tree of
+// additions for every token, wherever in a group it falls).  State: float32 [slot, heads, vdim,
+// dim] (column by column).
 #include "common.cuh"
 
 namespace {
 
 constexpr int LANES = 16;            // lanes that share a column
 constexpr int COLS = 8;              // columns of a block (four warps)
+constexpr int TB = 16;               // tokens of a group
+constexpr int THREADS = LANES * COLS;
 
+__device__ __forceinline__ void cp_async4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// Lane `sub` keeps NPL channels of its column in runs of R = min(NPL, 4): run j holds channels
+// j * 16 R + sub * R ... + R - 1, so that the 16 lanes' loads of a run are one contiguous stretch.
 template <int NPL>
-struct Tok {
-  float q[NPL], k[NPL], a[NPL], v;
+struct Runs {
+  static constexpr int R = NPL < 4 ? NPL : 4;
+  __device__ static __forceinline__ int channel(int sub, int i) { return (i / R) * (LANES * R) + sub * R + i % R; }
 };
 
-template <int NPL>
-__device__ __forceinline__ void load_tok(Tok<NPL>& t, const float* row, int q_off, int k_off, int v_off,
-                                         const float* arow, float a_head, int c0, int dim, int col, bool col_ok) {
-#pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int c = c0 + i;
-    const bool ok = c < dim;
-    t.q[i] = ok ? row[q_off + c] : 0.0f;
-    t.k[i] = ok ? row[k_off + c] : 0.0f;
-    t.a[i] = arow ? (ok ? arow[c] : 1.0f) : a_head;
-  }
-  t.v = col_ok ? row[v_off + col] : 0.0f;
-}
-
-template <int NPL>
-__global__ void __launch_bounds__(LANES * COLS)
+// STAGES groups of tokens in shared memory: one in use, the others on their way.
+template <int NPL, bool PER_CHANNEL, bool VEC, int STAGES>
+__global__ void __launch_bounds__(THREADS)
 linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
                    const float* __restrict__ head_decay, const int32_t* seq_row0, const int32_t* seq_slot,
                    int n_heads, int dim, int vdim, float* state, float* out) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int PAD = NPL * LANES;                      // channels with padding
+  constexpr int NARR = PER_CHANNEL ? 3 : 2;             // q, k (, decay)
+  constexpr int ROW = NARR * PAD + COLS;                // floats of a staged token
+  constexpr int R = Runs<NPL>::R;
   sb_pdl_launch();
   const int b = blockIdx.z, h = blockIdx.y;
-  const int sub = threadIdx.x % LANES;
-  const int col = blockIdx.x * COLS + threadIdx.x / LANES;
+  const int tid = threadIdx.x, sub = tid % LANES, cl = tid / LANES;
+  const int col0 = blockIdx.x * COLS, col = col0 + cl;
   const bool col_ok = col < vdim;
-  const int c0 = sub * NPL;
   const int row0 = seq_row0[b], n = seq_row0[b + 1] - row0;
   const int slot = seq_slot[b];
-  const float a_head = head_decay ? head_decay[h] : 1.0f;
+  const float a_head = PER_CHANNEL ? 1.0f : head_decay[h];
+  // padding channels and columns stay zero for good: cp.async writes the others only
+  if (dim < PAD || vdim - col0 < COLS) {
+    for (int i = tid; i < STAGES * TB * ROW; i += THREADS) smem[i] = 0.0f;
+    __syncthreads();
+  }
   sb_pdl_wait();
   float* srow = state + (((size_t)slot * n_heads + h) * vdim + (col_ok ? col : 0)) * dim;
   float S[NPL];
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) S[i] = (col_ok && c0 + i < dim) ? srow[c0 + i] : 0.0f;
-  const int qo = q_off + h * dim, ko = k_off + h * dim, vo = v_off + h * vdim;
+  for (int i = 0; i < NPL; ++i) {
+    const int c = Runs<NPL>::channel(sub, i);
+    S[i] = (col_ok && c < dim) ? srow[c] : 0.0f;
+  }
   const size_t per_row = (size_t)n_heads * dim;
-  Tok<NPL> cur, nxt;
-  if (n > 0)
-    load_tok<NPL>(cur, proj + (size_t)row0 * ld, qo, ko, vo,
-                  decay ? decay + (size_t)row0 * per_row + (size_t)h * dim : nullptr, a_head, c0, dim, col, col_ok);
-  for (int t = 0; t < n; ++t) {
-    if (t + 1 < n) {
-      const size_t r = (size_t)row0 + t + 1;
-      load_tok<NPL>(nxt, proj + r * ld, qo, ko, vo, decay ? decay + r * per_row + (size_t)h * dim : nullptr,
-                    a_head, c0, dim, col, col_ok);
-    }
-    float acc = 0.0f;
+  const int n_cols = min(COLS, vdim - col0);
+
+  // What this thread copies of every token, worked out once: piece k of the thread is 16 bytes
+  // (VEC) or one value of q, k, the decays or the block's values; `src[k]` points into the
+  // sequence's first row, `step[k]` is that tensor's row stride.
+  constexpr int V = VEC ? 4 : 1;
+  constexpr int PIECES = NARR * PAD / V + COLS / V;     // at most, per token
+  constexpr int MINE = (PIECES + THREADS - 1) / THREADS;
+  const float* src[MINE];
+  int dst[MINE], step[MINE], width[MINE];               // width: values of the piece (0: none)
+  {
+    const int per_arr = dim / V, n_vals = (n_cols + V - 1) / V;
 #pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      S[i] = fmaf(cur.a[i], S[i], cur.k[i] * cur.v);
-      acc = fmaf(S[i], cur.q[i], acc);
+    for (int k = 0; k < MINE; ++k) {
+      const int e = tid + k * THREADS;
+      const int arr = e / per_arr;
+      src[k] = proj, dst[k] = 0, step[k] = 0, width[k] = 0;
+      if (arr < NARR) {
+        const int c = (e - arr * per_arr) * V;
+        src[k] = arr == 0 ? proj + (size_t)row0 * ld + q_off + h * dim + c
+               : arr == 1 ? proj + (size_t)row0 * ld + k_off + h * dim + c
+                          : decay + (size_t)row0 * per_row + (size_t)h * dim + c;
+        step[k] = arr == 2 ? (int)per_row : ld;
+        dst[k] = arr * PAD + c;
+        width[k] = V;
+      } else if (e - NARR * per_arr < n_vals) {
+        const int c = (e - NARR * per_arr) * V;
+        src[k] = proj + (size_t)row0 * ld + v_off + h * vdim + col0 + c;
+        step[k] = ld;
+        dst[k] = NARR * PAD + c;
+        width[k] = min(V, n_cols - c);
+      }
     }
+  }
+  // stages tokens [t0, t0 + cnt) of the sequence into stage `st`
+  auto stage = [&](int st, int t0, int cnt) {
+    float* dst0 = smem + (size_t)st * TB * ROW;
 #pragma unroll
-    for (int o = LANES / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (sub == 0 && col_ok) out[((size_t)(row0 + t) * n_heads + h) * vdim + col] = acc;
-    cur = nxt;
+    for (int k = 0; k < MINE; ++k) {
+      if (width[k] == 0) continue;
+      const float* from = src[k] + (size_t)t0 * step[k];
+      float* to = dst0 + dst[k];
+      if (width[k] == 4) {
+        for (int tt = 0; tt < cnt; ++tt) cp_async16(to + tt * ROW, from + (size_t)tt * step[k]);
+      } else {
+        for (int tt = 0; tt < cnt; ++tt)
+          for (int u = 0; u < width[k]; ++u) cp_async4(to + tt * ROW + u, from + (size_t)tt * step[k] + u);
+      }
+    }
+    cp_commit();
+  };
+
+  const int n_groups = (n + TB - 1) / TB;
+  for (int g = 0; g < STAGES - 1; ++g) {
+    if (g < n_groups) stage(g, g * TB, min(TB, n - g * TB));
+    else cp_commit();
+  }
+  for (int g = 0; g < n_groups; ++g) {
+    const int t0 = g * TB, cnt = min(TB, n - t0);
+    cp_wait<STAGES - 2>();                              // group g has landed (for this thread's copies)
+    __syncthreads();                                    // ... for everybody's, and group g - 1 is no longer read
+    {
+      const int g2 = g + STAGES - 1;
+      if (g2 < n_groups) stage(g2 % STAGES, g2 * TB, min(TB, n - g2 * TB));
+      else cp_commit();
+    }
+    const float* base = smem + (size_t)(g % STAGES) * TB * ROW;
+    float acc[TB];
+#pragma unroll
+    for (int tt = 0; tt < TB; ++tt) {
+      acc[tt] = 0.0f;
+      if (tt < cnt) {
+        const float* tok = base + tt * ROW;
+        const float v = tok[NARR * PAD + cl];
+        float a = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NPL / R; ++j) {
+          float qv[R], kv[R], av[R];
+          const int c = j * (LANES * R) + sub * R;
+          if (R == 4) {
+            *reinterpret_cast<float4*>(qv) = *reinterpret_cast<const float4*>(tok + c);
+            *reinterpret_cast<float4*>(kv) = *reinterpret_cast<const float4*>(tok + PAD + c);
+            if (PER_CHANNEL) *reinterpret_cast<float4*>(av) = *reinterpret_cast<const float4*>(tok + 2 * PAD + c);
+          } else {
+#pragma unroll
+            for (int u = 0; u < R; ++u) {
+              qv[u] = tok[c + u];
+              kv[u] = tok[PAD + c + u];
+              if (PER_CHANNEL) av[u] = tok[2 * PAD + c + u];
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < R; ++u) {
+            const float s = fmaf(PER_CHANNEL ? av[u] : a_head, S[j * R + u], kv[u] * v);
+            S[j * R + u] = s;
+            a = fmaf(s, qv[u], a);
+          }
+        }
+        acc[tt] = a;
+      }
+    }
+    // the lanes' partial sums of the group's tokens, added so that lane i ends with token i's sum:
+    // at every step a lane keeps the half of its values whose token number has the step's bit as
+    // the lane has it, and gets the partner's sums of those tokens
+#pragma unroll
+    for (int w = TB / 2; w > 0; w >>= 1) {
+      const bool up = sub & w;
+#pragma unroll
+      for (int i = 0; i < w; ++i) {
+        const float keep = up ? acc[i + w] : acc[i];
+        const float give = up ? acc[i] : acc[i + w];
+        acc[i] = keep + __shfl_xor_sync(0xffffffffu, give, w);
+      }
+    }
+    if (sub < cnt && col_ok) out[((size_t)(row0 + t0 + sub) * n_heads + h) * vdim + col] = acc[0];
   }
   if (col_ok) {
 #pragma unroll
-    for (int i = 0; i < NPL; ++i)
-      if (c0 + i < dim) srow[c0 + i] = S[i];
+    for (int i = 0; i < NPL; ++i) {
+      const int c = Runs<NPL>::channel(sub, i);
+      if (c < dim) srow[c] = S[i];
+    }
   }
+}
+
+template <int NPL>
+constexpr size_t scan_smem(bool per_channel, int stages) {
+  return (size_t)stages * TB * ((per_channel ? 3 : 2) * NPL * LANES + COLS) * sizeof(float);
+}
+
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 1;
+  }
+  return n;
+}
+
+// Blocks that fit the GPU at once with this much shared memory each.
+long fits(size_t smem) {
+  const long per_sm = (long)((227 * 1024) / (smem + 1024));
+  return (long)sm_count() * (per_sm < 16 ? per_sm : 16);
+}
+
+template <int NPL, bool PC, bool VEC, int STAGES>
+cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
+                        const float* decay, const float* head_decay, const int32_t* seq_row0,
+                        const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
+  constexpr size_t smem = scan_smem<NPL>(PC, STAGES);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(linrec_scan_kernel<NPL, PC, VEC, STAGES>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  configured = true;
+  return sb_launch<SB_K_OTHER>(linrec_scan_kernel<NPL, PC, VEC, STAGES>, grid, dim3(THREADS), smem, stream, proj, ld,
+                               q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
+}
+
+// Three stages, unless the grid then needs a second wave of blocks that two stages spare it.
+template <int NPL, bool PC, bool VEC>
+cudaError_t launch_scan_staged(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
+                               int v_off, const float* decay, const float* head_decay, const int32_t* seq_row0,
+                               const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
+  const long blocks = (long)grid.x * grid.y * grid.z;
+  if (blocks > fits(scan_smem<NPL>(PC, 3)) && blocks <= fits(scan_smem<NPL>(PC, 2)))
+    return launch_scan<NPL, PC, VEC, 2>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                        seq_slot, n_heads, dim, vdim, state, out);
+  return launch_scan<NPL, PC, VEC, 3>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                      seq_slot, n_heads, dim, vdim, state, out);
 }
 
 }  // namespace
@@ -101,15 +264,21 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
   if (n_heads > 65535 || n_seqs > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: %d heads, %d sequences", n_heads, n_seqs);
   const dim3 grid((vdim + COLS - 1) / COLS, n_heads, n_seqs);
   const int npl = (dim + LANES - 1) / LANES;
-#define SB_LINREC_LAUNCH(N)                                                                                   \
-  sb_launch<SB_K_OTHER>(linrec_scan_kernel<N>, grid, dim3(LANES * COLS), 0, stream, proj, ld, q_off, k_off,  \
-                        v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out)
+  // 16-byte copies when every staged stretch starts on a 16-byte boundary
+  const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
+                   !((uintptr_t)proj & 15) && !((uintptr_t)decay & 15);
+  cudaError_t e;
+#define SB_LINREC_ARGS grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out
+#define SB_LINREC_LAUNCH(N)                                                                   \
+  e = decay ? (vec ? launch_scan_staged<N, true, true>(SB_LINREC_ARGS) : launch_scan_staged<N, true, false>(SB_LINREC_ARGS)) \
+            : (vec ? launch_scan_staged<N, false, true>(SB_LINREC_ARGS) : launch_scan_staged<N, false, false>(SB_LINREC_ARGS))
   if (npl <= 1) SB_LINREC_LAUNCH(1);
   else if (npl <= 2) SB_LINREC_LAUNCH(2);
   else if (npl <= 4) SB_LINREC_LAUNCH(4);
   else if (npl <= 8) SB_LINREC_LAUNCH(8);
   else SB_LINREC_LAUNCH(16);
 #undef SB_LINREC_LAUNCH
-  SB_CHECK_LAUNCH("sb_linrec_scan");
+#undef SB_LINREC_ARGS
+  if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_linrec_scan: launch failed: %s", cudaGetErrorString(e));
   return SB_OK;
 }

@@ -104,13 +104,6 @@ __device__ __forceinline__ void pair_of(int c, int rot, int interleaved, int& i,
   }
 }
 
-// The rotated value of element c given itself (`mine`) and its partner (`theirs`).
-__device__ __forceinline__ float turned(float mine, float theirs, bool first, float angle) {
-  float s, co;
-  sincosf(angle, &s, &co);
-  return first ? sb_rot_lo(mine, theirs, co, s) : sb_rot_hi(theirs, mine, co, s);
-}
-
 __device__ __forceinline__ int page_of(const int32_t* page_off, const int32_t* page_ids, int seq, int pos,
                                        int page_size) {
   const int first = page_off[seq], n = page_off[seq + 1] - first;
@@ -137,6 +130,48 @@ struct PrepArgs {
   void* q_out;
 };
 
+// Rotates the first `rot` values of `heads` vectors of `n_in` values each (read through `get(head,
+// c)`) by the angles fpos * inv_freq[i] and hands every finished value to `put(head, c, value)`;
+// values from `rot` on pass as they are, and values from n_in up to n_out are zeros.  A thread keeps
+// to one pair and walks over the heads, so the pair's sine and cosine are worked out once.
+template <int NT, typename Get, typename Put>
+__device__ __forceinline__ void turn_heads(int heads, int n_in, int n_out, int rot, int interleaved,
+                                           const float* __restrict__ inv_freq, float fpos, Get get, Put put) {
+  const int n_pairs = rot >> 1;
+  if (n_pairs > 0) {
+    const int groups = NT / n_pairs > 0 ? NT / n_pairs : 1;      // thread groups that take heads in turn
+    const int i = threadIdx.x % n_pairs, first_head = threadIdx.x / n_pairs;
+    if (n_pairs <= NT) {
+      if (first_head < groups) {
+        float sn, cs;
+        sincosf(fpos * inv_freq[i], &sn, &cs);
+        const int lo = interleaved ? 2 * i : i, hi = interleaved ? 2 * i + 1 : i + n_pairs;
+        for (int h = first_head; h < heads; h += groups) {
+          const float a = get(h, lo), b = get(h, hi);
+          put(h, lo, sb_rot_lo(a, b, cs, sn));
+          put(h, hi, sb_rot_hi(a, b, cs, sn));
+        }
+      }
+    } else {
+      for (int j = threadIdx.x; j < n_pairs; j += NT) {          // more pairs than threads
+        float sn, cs;
+        sincosf(fpos * inv_freq[j], &sn, &cs);
+        const int lo = interleaved ? 2 * j : j, hi = interleaved ? 2 * j + 1 : j + n_pairs;
+        for (int h = 0; h < heads; ++h) {
+          const float a = get(h, lo), b = get(h, hi);
+          put(h, lo, sb_rot_lo(a, b, cs, sn));
+          put(h, hi, sb_rot_hi(a, b, cs, sn));
+        }
+      }
+    }
+  }
+  const int rest = n_out - rot;
+  for (int e = threadIdx.x; e < heads * rest; e += NT) {
+    const int h = e / rest, c = rot + e % rest;
+    put(h, c, c < n_in ? get(h, c) : 0.0f);
+  }
+}
+
 // blockIdx.y: 0 queries, 1 keys, 2 values.
 template <int NT, typename TW, typename TQ, typename TC>
 __global__ void __launch_bounds__(NT) attn_prep_kernel(const PrepArgs p) {
@@ -155,80 +190,57 @@ __global__ void __launch_bounds__(NT) attn_prep_kernel(const PrepArgs p) {
   if (what == 2) {
     // values: the v section, or the raw key projection; rotated over all vdim when a table is given
     const float* src = row + (p.v_off >= 0 ? p.v_off : p.k_off);
-    TC* cache = reinterpret_cast<TC*>(p.cache);
-    for (int e = threadIdx.x; e < p.n_kv_heads * p.hd; e += NT) {
-      const int head = e / p.hd, c = e % p.hd;
-      float v = 0.0f;
-      if (c < p.vdim) {
-        v = src[head * p.vdim + c];
-        if (p.v_inv_freq) {
-          int i, other;
-          bool first;
-          pair_of(c, p.vdim, p.interleaved, i, first, other);
-          if (other < p.vdim) v = turned(v, src[head * p.vdim + other], first, fpos * p.v_inv_freq[i]);
-        }
-      }
-      const size_t dst = (((size_t)page * 2 + 1) * p.n_kv_heads + head) * p.page_size + pos % p.page_size;
-      cache[dst * p.hd + c] = sb_from_f32<TC>(v);
-    }
+    TC* dst = reinterpret_cast<TC*>(p.cache) +
+              ((((size_t)page * 2 + 1) * p.n_kv_heads) * p.page_size + pos % p.page_size) * p.hd;
+    const size_t head_step = (size_t)p.page_size * p.hd;
+    const int vdim = p.vdim;
+    turn_heads<NT>(p.n_kv_heads, vdim, p.hd, p.v_inv_freq ? vdim : 0, p.interleaved, p.v_inv_freq, fpos,
+                   [&](int h, int c) { return src[h * vdim + c]; },
+                   [&](int h, int c, float v) { dst[h * head_step + c] = sb_from_f32<TC>(v); });
     return;
   }
   const int heads = what == 0 ? p.n_q_heads : p.n_kv_heads;
   const float* src = row + (what == 0 ? p.q_off : p.k_off);
   const TW* nw = reinterpret_cast<const TW*>(what == 0 ? p.q_norm : p.k_norm);
+  const int dim = p.dim;
   float inv = 1.0f;
   if (nw) {
     float s = 0.0f;
-    for (int e = threadIdx.x; e < heads * p.dim; e += NT) s = fmaf(src[e], src[e], s);
-    inv = 1.0f / sqrtf(block_sum<NT>(s, red) / (float)(heads * p.dim) + p.eps);
+    for (int e = threadIdx.x; e < heads * dim; e += NT) s = fmaf(src[e], src[e], s);
+    inv = 1.0f / sqrtf(block_sum<NT>(s, red) / (float)(heads * dim) + p.eps);
   }
-  for (int e = threadIdx.x; e < heads * p.hd; e += NT) {
-    const int head = e / p.hd, c = e % p.hd;
-    float v = 0.0f;
-    if (c < p.dim) {
-      const int at = head * p.dim + c;
-      v = src[at];
-      if (nw) v = (v * inv) * sb_to_f32<TW>(nw[at]);
-      if (c < p.rot) {
-        int i, other;
-        bool first;
-        pair_of(c, p.rot, p.interleaved, i, first, other);
-        float w = src[head * p.dim + other];
-        if (nw) w = (w * inv) * sb_to_f32<TW>(nw[head * p.dim + other]);
-        v = turned(v, w, first, fpos * p.inv_freq[i]);
-      }
-    }
-    if (what == 0) {
-      reinterpret_cast<TQ*>(p.q_out)[((size_t)t * p.n_q_heads + head) * p.hd + c] = sb_from_f32<TQ>(v);
-    } else {
-      const size_t dst = (((size_t)page * 2) * p.n_kv_heads + head) * p.page_size + pos % p.page_size;
-      reinterpret_cast<TC*>(p.cache)[dst * p.hd + c] = sb_from_f32<TC>(v);
-    }
+  auto get = [&](int h, int c) {
+    const float v = src[h * dim + c];
+    return nw ? (v * inv) * sb_to_f32<TW>(nw[h * dim + c]) : v;
+  };
+  if (what == 0) {
+    TQ* dst = reinterpret_cast<TQ*>(p.q_out) + (size_t)t * p.n_q_heads * p.hd;
+    const int hd = p.hd;
+    turn_heads<NT>(heads, dim, hd, p.rot, p.interleaved, p.inv_freq, fpos, get,
+                   [&](int h, int c, float v) { dst[h * hd + c] = sb_from_f32<TQ>(v); });
+  } else {
+    TC* dst = reinterpret_cast<TC*>(p.cache) +
+              ((((size_t)page * 2) * p.n_kv_heads) * p.page_size + pos % p.page_size) * p.hd;
+    const size_t head_step = (size_t)p.page_size * p.hd;
+    turn_heads<NT>(heads, dim, p.hd, p.rot, p.interleaved, p.inv_freq, fpos, get,
+                   [&](int h, int c, float v) { dst[h * head_step + c] = sb_from_f32<TC>(v); });
   }
 }
 
-template <typename T>
-__global__ void attn_unrotate_kernel(const T* in, T* out, size_t n, int n_heads, int hd, int vdim,
-                                     int interleaved, const float* __restrict__ v_inv_freq,
-                                     const int32_t* row_pos) {
+// One block per row: the first vdim values of every head, turned back by the row's position.
+template <int NT, typename T>
+__global__ void __launch_bounds__(NT)
+attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int interleaved,
+                     const float* __restrict__ v_inv_freq, const int32_t* row_pos) {
   sb_pdl_launch();
+  const size_t t = blockIdx.x;
+  const float fpos = v_inv_freq ? -(float)row_pos[t] : 0.0f;
   sb_pdl_wait();
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
-    const int c = (int)(e % vdim);
-    const size_t rh = e / vdim;                       // row * heads + head
-    const T* src = in + rh * hd;
-    float v = sb_to_f32<T>(src[c]);
-    if (v_inv_freq) {
-      int i, other;
-      bool first;
-      pair_of(c, vdim, interleaved, i, first, other);
-      if (other < vdim) {
-        const float pos = (float)row_pos[rh / n_heads];
-        v = turned(v, sb_to_f32<T>(src[other]), first, -(pos * v_inv_freq[i]));
-      }
-    }
-    out[e] = sb_from_f32<T>(v);
-  }
+  const T* src = in + t * n_heads * hd;
+  T* dst = out + t * n_heads * vdim;
+  turn_heads<NT>(n_heads, vdim, vdim, v_inv_freq ? vdim : 0, interleaved, v_inv_freq, fpos,
+                 [&](int h, int c) { return sb_to_f32<T>(src[h * hd + c]); },
+                 [&](int h, int c, float v) { dst[h * vdim + c] = sb_from_f32<T>(v); });
 }
 
 // ---------------------------------------------------------------------- linear recurrence
@@ -306,12 +318,16 @@ extern "C" int sb_stream_add(const float* x, const float* add, const void* vec, 
   if (n_rows <= 0 || width <= 0 || !x || !out) SB_FAIL(SB_ERR_ARG, "sb_stream_add: rows=%d width=%d", n_rows, width);
   if ((vec && !sb_valid_dtype(vec_dtype)) || (normed && (!next_w || !sb_valid_dtype(next_w_dtype) || !sb_valid_dtype(normed_dtype))))
     SB_FAIL(SB_ERR_ARG, "sb_stream_add: dtype codes %d %d %d", vec_dtype, next_w_dtype, normed_dtype);
-  constexpr int NT = 256;
+  // few rows (decode): more threads a row, so that a row's loads are in flight together
   SB_DISPATCH_DTYPE(vec ? vec_dtype : SB_F32, TV, {
     SB_DISPATCH_DTYPE(normed ? next_w_dtype : SB_F32, TN, {
       SB_DISPATCH_DTYPE(normed ? normed_dtype : SB_F32, TO, {
-        sb_launch<SB_K_ELEMENTWISE>(stream_add_kernel<NT, TV, TN, TO>, dim3(n_rows), dim3(NT), 0, stream, x, add,
-                                    (const TV*)vec, width, out, (const TN*)next_w, next_eps, (TO*)normed);
+        if (n_rows >= 512 || width <= 1024)
+          sb_launch<SB_K_ELEMENTWISE>(stream_add_kernel<256, TV, TN, TO>, dim3(n_rows), dim3(256), 0, stream, x, add,
+                                      (const TV*)vec, width, out, (const TN*)next_w, next_eps, (TO*)normed);
+        else
+          sb_launch<SB_K_ELEMENTWISE>(stream_add_kernel<1024, TV, TN, TO>, dim3(n_rows), dim3(1024), 0, stream, x, add,
+                                      (const TV*)vec, width, out, (const TN*)next_w, next_eps, (TO*)normed);
       });
     });
   });
@@ -383,10 +399,9 @@ extern "C" int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows
   if (n_rows <= 0 || n_heads <= 0 || vdim <= 0 || hd < vdim || !in || !out || !sb_valid_dtype(dtype))
     SB_FAIL(SB_ERR_ARG, "sb_attn_unrotate: rows=%d heads=%d hd=%d vdim=%d dtype=%d", n_rows, n_heads, hd, vdim, dtype);
   if (v_inv_freq && (vdim % 2 || !row_pos)) SB_FAIL(SB_ERR_ARG, "sb_attn_unrotate: rotation needs an even vdim and positions");
-  const size_t n = (size_t)n_rows * n_heads * vdim;
   SB_DISPATCH_DTYPE(dtype, T, {
-    sb_launch<SB_K_ELEMENTWISE>(attn_unrotate_kernel<T>, dim3(grid_for(n, 256)), dim3(256), 0, stream, (const T*)in,
-                                (T*)out, n, n_heads, hd, vdim, interleaved, v_inv_freq, row_pos);
+    sb_launch<SB_K_ELEMENTWISE>(attn_unrotate_kernel<256, T>, dim3(n_rows), dim3(256), 0, stream, (const T*)in, (T*)out,
+                                n_heads, hd, vdim, interleaved, v_inv_freq, row_pos);
   });
   SB_CHECK_LAUNCH("sb_attn_unrotate");
   return SB_OK;
