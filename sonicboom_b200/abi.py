@@ -57,6 +57,7 @@ CORE = {
     "sb_attn_unrotate": ("i", "ppiiiiiipps"),
     "sb_linrec_prep": ("i", "piiiiiiffiipppfs"),
     "sb_linrec_scan": ("i", "piiiippippiiipps"),
+    "sb_linrec_force_columns": ("v", "i"),
     "sb_linrec_out": ("i", "ppiiiiipifpis"),
     "sb_sample_params_size": ("i", ""),
     "sb_sample": ("i", "piippipps"),

@@ -8,8 +8,9 @@
 // channel) read from a tensor, or one fixed value per head.
 //
 // A column of S (the `dim` values that belong to one value channel) is shared by 16 lanes that
-// keep their runs of it in registers for the whole step; a warp holds two columns, a block
-// eight.  Tokens come in groups of 16: a group's q, k, decays and the block's values are staged in
+// keep their runs of it in registers for the whole step (of one column, or of two neighbouring
+// ones when the step has blocks enough: what a lane reads of a token then serves both); a block
+// has eight such groups of lanes.  Tokens come in groups of 16: a group's q, k, decays and the block's values are staged in
 // shared memory with cp.async one or two groups ahead of the one that is computed; per token a
 // lane multiplies and adds its runs, and the 16 lanes' partial dot products of the group's 16
 // tokens are added in 15 exchanges, after which lane i holds token i's sum (the same tree of
@@ -20,9 +21,9 @@
 namespace {
 
 constexpr int LANES = 16;            // lanes that share a column
-constexpr int COLS = 8;              // columns of a block (four warps)
+constexpr int GROUPS = 8;            // groups of 16 lanes in a block (four warps)
 constexpr int TB = 16;               // tokens of a group
-constexpr int THREADS = LANES * COLS;
+constexpr int THREADS = LANES * GROUPS;
 
 __device__ __forceinline__ void cp_async4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
@@ -43,7 +44,9 @@ struct Runs {
 };
 
 // STAGES groups of tokens in shared memory: one in use, the others on their way.
-template <int NPL, bool PER_CHANNEL, bool VEC, int STAGES>
+// CPT columns per thread: a lane keeps its runs of CPT neighbouring columns, so that what it reads of
+// a token's q, k and decays serves CPT columns.
+template <int NPL, bool PER_CHANNEL, bool VEC, int STAGES, int CPT>
 __global__ void __launch_bounds__(THREADS)
 linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, const float* decay,
                    const float* __restrict__ head_decay, const int32_t* seq_row0, const int32_t* seq_slot,
@@ -51,13 +54,13 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
   extern __shared__ __align__(16) float smem[];
   constexpr int PAD = NPL * LANES;                      // channels with padding
   constexpr int NARR = PER_CHANNEL ? 3 : 2;             // q, k (, decay)
-  constexpr int ROW = NARR * PAD + COLS;                // floats of a staged token
   constexpr int R = Runs<NPL>::R;
+  constexpr int COLS = GROUPS * CPT;                   // columns of a block
+  constexpr int ROW = NARR * PAD + COLS;                // floats of a staged token
   sb_pdl_launch();
   const int b = blockIdx.z, h = blockIdx.y;
   const int tid = threadIdx.x, sub = tid % LANES, cl = tid / LANES;
-  const int col0 = blockIdx.x * COLS, col = col0 + cl;
-  const bool col_ok = col < vdim;
+  const int col0 = blockIdx.x * COLS, col = col0 + cl * CPT;      // this thread's first column
   const int row0 = seq_row0[b], n = seq_row0[b + 1] - row0;
   const int slot = seq_slot[b];
   const float a_head = PER_CHANNEL ? 1.0f : head_decay[h];
@@ -67,13 +70,15 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
     __syncthreads();
   }
   sb_pdl_wait();
-  float* srow = state + (((size_t)slot * n_heads + h) * vdim + (col_ok ? col : 0)) * dim;
-  float S[NPL];
+  float* srow = state + (((size_t)slot * n_heads + h) * vdim) * dim;
+  float S[CPT][NPL];
 #pragma unroll
-  for (int i = 0; i < NPL; ++i) {
-    const int c = Runs<NPL>::channel(sub, i);
-    S[i] = (col_ok && c < dim) ? srow[c] : 0.0f;
-  }
+  for (int x = 0; x < CPT; ++x)
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int c = Runs<NPL>::channel(sub, i);
+      S[x][i] = (col + x < vdim && c < dim) ? srow[(size_t)(col + x) * dim + c] : 0.0f;
+    }
   const size_t per_row = (size_t)n_heads * dim;
   const int n_cols = min(COLS, vdim - col0);
 
@@ -142,14 +147,16 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
       else cp_commit();
     }
     const float* base = smem + (size_t)(g % STAGES) * TB * ROW;
-    float acc[TB];
+    float acc[CPT][TB];
 #pragma unroll
     for (int tt = 0; tt < TB; ++tt) {
-      acc[tt] = 0.0f;
+#pragma unroll
+      for (int x = 0; x < CPT; ++x) acc[x][tt] = 0.0f;
       if (tt < cnt) {
         const float* tok = base + tt * ROW;
-        const float v = tok[NARR * PAD + cl];
-        float a = 0.0f;
+        float v[CPT];
+#pragma unroll
+        for (int x = 0; x < CPT; ++x) v[x] = tok[NARR * PAD + cl * CPT + x];
 #pragma unroll
         for (int j = 0; j < NPL / R; ++j) {
           float qv[R], kv[R], av[R];
@@ -167,42 +174,48 @@ linrec_scan_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, c
             }
           }
 #pragma unroll
-          for (int u = 0; u < R; ++u) {
-            const float s = fmaf(PER_CHANNEL ? av[u] : a_head, S[j * R + u], kv[u] * v);
-            S[j * R + u] = s;
-            a = fmaf(s, qv[u], a);
-          }
+          for (int x = 0; x < CPT; ++x)
+#pragma unroll
+            for (int u = 0; u < R; ++u) {
+              const float sv = fmaf(PER_CHANNEL ? av[u] : a_head, S[x][j * R + u], kv[u] * v[x]);
+              S[x][j * R + u] = sv;
+              acc[x][tt] = fmaf(sv, qv[u], acc[x][tt]);
+            }
         }
-        acc[tt] = a;
       }
     }
     // the lanes' partial sums of the group's tokens, added so that lane i ends with token i's sum:
     // at every step a lane keeps the half of its values whose token number has the step's bit as
     // the lane has it, and gets the partner's sums of those tokens
 #pragma unroll
-    for (int w = TB / 2; w > 0; w >>= 1) {
-      const bool up = sub & w;
+    for (int x = 0; x < CPT; ++x) {
 #pragma unroll
-      for (int i = 0; i < w; ++i) {
-        const float keep = up ? acc[i + w] : acc[i];
-        const float give = up ? acc[i] : acc[i + w];
-        acc[i] = keep + __shfl_xor_sync(0xffffffffu, give, w);
+      for (int w = TB / 2; w > 0; w >>= 1) {
+        const bool up = sub & w;
+#pragma unroll
+        for (int i = 0; i < w; ++i) {
+          const float keep = up ? acc[x][i + w] : acc[x][i];
+          const float give = up ? acc[x][i] : acc[x][i + w];
+          acc[x][i] = keep + __shfl_xor_sync(0xffffffffu, give, w);
+        }
       }
+      if (sub < cnt && col + x < vdim) out[((size_t)(row0 + t0 + sub) * n_heads + h) * vdim + col + x] = acc[x][0];
     }
-    if (sub < cnt && col_ok) out[((size_t)(row0 + t0 + sub) * n_heads + h) * vdim + col] = acc[0];
   }
-  if (col_ok) {
+#pragma unroll
+  for (int x = 0; x < CPT; ++x) {
+    if (col + x >= vdim) continue;
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
       const int c = Runs<NPL>::channel(sub, i);
-      if (c < dim) srow[c] = S[i];
+      if (c < dim) srow[(size_t)(col + x) * dim + c] = S[x][i];
     }
   }
 }
 
 template <int NPL>
-constexpr size_t scan_smem(bool per_channel, int stages) {
-  return (size_t)stages * TB * ((per_channel ? 3 : 2) * NPL * LANES + COLS) * sizeof(float);
+constexpr size_t scan_smem(bool per_channel, int stages, int cpt) {
+  return (size_t)stages * TB * ((per_channel ? 3 : 2) * NPL * LANES + GROUPS * cpt) * sizeof(float);
 }
 
 int sm_count() {
@@ -221,33 +234,53 @@ long fits(size_t smem) {
   return (long)sm_count() * (per_sm < 16 ? per_sm : 16);
 }
 
-template <int NPL, bool PC, bool VEC, int STAGES>
+template <int NPL, bool PC, bool VEC, int STAGES, int CPT>
 cudaError_t launch_scan(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off, int v_off,
                         const float* decay, const float* head_decay, const int32_t* seq_row0,
                         const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
-  constexpr size_t smem = scan_smem<NPL>(PC, STAGES);
+  constexpr size_t smem = scan_smem<NPL>(PC, STAGES, CPT);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(linrec_scan_kernel<NPL, PC, VEC, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(linrec_scan_kernel<NPL, PC, VEC, STAGES, CPT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
   configured = true;
-  return sb_launch<SB_K_OTHER>(linrec_scan_kernel<NPL, PC, VEC, STAGES>, grid, dim3(THREADS), smem, stream, proj, ld,
+  return sb_launch<SB_K_OTHER>(linrec_scan_kernel<NPL, PC, VEC, STAGES, CPT>, grid, dim3(THREADS), smem, stream, proj, ld,
                                q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
 }
 
 // Three stages, unless the grid then needs a second wave of blocks that two stages spare it.
-template <int NPL, bool PC, bool VEC>
-cudaError_t launch_scan_staged(dim3 grid, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
+template <int NPL, bool PC, bool VEC, int CPT>
+cudaError_t launch_scan_staged(int n_seqs, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
                                int v_off, const float* decay, const float* head_decay, const int32_t* seq_row0,
                                const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
+  const dim3 grid((vdim + GROUPS * CPT - 1) / (GROUPS * CPT), n_heads, n_seqs);
   const long blocks = (long)grid.x * grid.y * grid.z;
-  if (blocks > fits(scan_smem<NPL>(PC, 3)) && blocks <= fits(scan_smem<NPL>(PC, 2)))
-    return launch_scan<NPL, PC, VEC, 2>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
-                                        seq_slot, n_heads, dim, vdim, state, out);
-  return launch_scan<NPL, PC, VEC, 3>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
-                                      seq_slot, n_heads, dim, vdim, state, out);
+  if (blocks > fits(scan_smem<NPL>(PC, 3, CPT)) && blocks <= fits(scan_smem<NPL>(PC, 2, CPT)))
+    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                             seq_slot, n_heads, dim, vdim, state, out);
+  return launch_scan<NPL, PC, VEC, 3, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                           seq_slot, n_heads, dim, vdim, state, out);
+}
+
+int g_force_cpt = 0;
+
+// Columns per thread: two when that still gives half of the SMs a block, else one.  Measured on
+// B200, 2,048 tokens of one sequence, key size 128, 256 value channels a head: 8 heads (128 blocks
+// of two columns a thread) 238 us against 303 us with one column, 14 heads 324 against 506 us;
+// 6 heads of 64 x 64 (24 blocks) 173 against 156 us.
+template <int NPL, bool PC, bool VEC>
+cudaError_t launch_scan_cols(int n_seqs, cudaStream_t stream, const float* proj, int ld, int q_off, int k_off,
+                             int v_off, const float* decay, const float* head_decay, const int32_t* seq_row0,
+                             const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
+  const long blocks2 = (long)((vdim + 2 * GROUPS - 1) / (2 * GROUPS)) * n_heads * n_seqs;
+  const bool two = g_force_cpt ? g_force_cpt == 2 : (NPL <= 8 && 2 * blocks2 >= sm_count());
+  if (two)
+    return launch_scan_staged<NPL, PC, VEC, (NPL <= 8 ? 2 : 1)>(n_seqs, stream, proj, ld, q_off, k_off, v_off, decay,
+                                                                 head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out);
+  return launch_scan_staged<NPL, PC, VEC, 1>(n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                             seq_slot, n_heads, dim, vdim, state, out);
 }
 
 }  // namespace
@@ -262,16 +295,15 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
     SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: exactly one of the two kinds of decay is given");
   if (dim > 16 * LANES) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: key size %d is above %d", dim, 16 * LANES);
   if (n_heads > 65535 || n_seqs > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: %d heads, %d sequences", n_heads, n_seqs);
-  const dim3 grid((vdim + COLS - 1) / COLS, n_heads, n_seqs);
   const int npl = (dim + LANES - 1) / LANES;
   // 16-byte copies when every staged stretch starts on a 16-byte boundary
   const bool vec = dim % 4 == 0 && vdim % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
                    !((uintptr_t)proj & 15) && !((uintptr_t)decay & 15);
   cudaError_t e;
-#define SB_LINREC_ARGS grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out
+#define SB_LINREC_ARGS n_seqs, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0, seq_slot, n_heads, dim, vdim, state, out
 #define SB_LINREC_LAUNCH(N)                                                                   \
-  e = decay ? (vec ? launch_scan_staged<N, true, true>(SB_LINREC_ARGS) : launch_scan_staged<N, true, false>(SB_LINREC_ARGS)) \
-            : (vec ? launch_scan_staged<N, false, true>(SB_LINREC_ARGS) : launch_scan_staged<N, false, false>(SB_LINREC_ARGS))
+  e = decay ? (vec ? launch_scan_cols<N, true, true>(SB_LINREC_ARGS) : launch_scan_cols<N, true, false>(SB_LINREC_ARGS)) \
+            : (vec ? launch_scan_cols<N, false, true>(SB_LINREC_ARGS) : launch_scan_cols<N, false, false>(SB_LINREC_ARGS))
   if (npl <= 1) SB_LINREC_LAUNCH(1);
   else if (npl <= 2) SB_LINREC_LAUNCH(2);
   else if (npl <= 4) SB_LINREC_LAUNCH(4);
@@ -282,3 +314,6 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
   if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_linrec_scan: launch failed: %s", cudaGetErrorString(e));
   return SB_OK;
 }
+
+// For measurements and tests: 1 or 2 columns per thread for every call, 0 by the sizes again.
+extern "C" void sb_linrec_force_columns(int cpt) { g_force_cpt = cpt == 1 || cpt == 2 ? cpt : 0; }

@@ -238,6 +238,23 @@ attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int int
   sb_pdl_wait();
   const T* src = in + t * n_heads * hd;
   T* dst = out + t * n_heads * vdim;
+  if constexpr (sizeof(T) == 2) {
+    // neighbouring pairs of 16-bit values: a pair is one 4-byte access
+    const int n_pairs = vdim >> 1;
+    if (v_inv_freq && interleaved && !(hd & 1) && !(vdim & 1) && n_pairs <= NT) {
+      const int groups = NT / n_pairs, i = threadIdx.x % n_pairs, first_head = threadIdx.x / n_pairs;
+      if (first_head >= groups) return;
+      float sn, cs;
+      sincosf(fpos * v_inv_freq[i], &sn, &cs);
+      const __nv_bfloat162* src2 = reinterpret_cast<const __nv_bfloat162*>(src);
+      __nv_bfloat162* dst2 = reinterpret_cast<__nv_bfloat162*>(dst);
+      for (int h = first_head; h < n_heads; h += groups) {
+        const float2 ab = __bfloat1622float2(src2[h * (hd >> 1) + i]);
+        dst2[h * n_pairs + i] = __floats2bfloat162_rn(sb_rot_lo(ab.x, ab.y, cs, sn), sb_rot_hi(ab.x, ab.y, cs, sn));
+      }
+      return;
+    }
+  }
   turn_heads<NT>(n_heads, vdim, vdim, v_inv_freq ? vdim : 0, interleaved, v_inv_freq, fpos,
                  [&](int h, int c) { return sb_to_f32<T>(src[h * hd + c]); },
                  [&](int h, int c, float v) { dst[h * vdim + c] = sb_from_f32<T>(v); });

@@ -249,6 +249,7 @@ int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, int v_off, c
                    const float* head_decay, int n_seqs, const int32_t* seq_row0,
                    const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state,
                    float* out, sb_stream_t stream);
+void sb_linrec_force_columns(int cpt);   /* 1 or 2 columns per thread in sb_linrec_scan; 0: by the sizes */
 /* out [rows, n_heads * vdim] = o / sqrt(mean over vdim of o^2 + eps) * norm_w[vdim] (optional) *
  * silu(g), g at g_off of the projection row. */
 int sb_linrec_out(const float* o, const float* proj, int n_rows, int ld, int g_off, int n_heads,

@@ -847,6 +847,12 @@ def linrec_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, plan, n_
     return out
 
 
+def force_linrec_columns(cpt: int) -> None:
+    """1 or 2: every `linrec_scan` keeps that many columns of the state per thread (for measurements
+    and tests; the results are the same bits); 0: chosen by the sizes again."""
+    lib().sb_linrec_force_columns(int(cpt))
+
+
 def linrec_out(o: torch.Tensor, proj: torch.Tensor, g_off: int, n_heads: int, vdim: int,
                norm_w: torch.Tensor | None, eps: float, out: torch.Tensor) -> torch.Tensor:
     """out [rows, heads * vdim] = rms(o) per head (optional weight [vdim]) * silu(g of the row)."""

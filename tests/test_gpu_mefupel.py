@@ -276,6 +276,15 @@ def test_linear_recurrence_kernels(H, d, dv):
         whole = scan(xs, H, d, dv, None, hd, state, [4, 1], z=zs if kind == "channel" else None, **kw)
         assert rel_err(whole[:T], refs[0]) < 1e-5 and rel_err(whole[T:], refs[1]) < 1e-5
         assert float(state[[0, 2, 3, 5]].abs().max()) == 0.0
+        # one or two columns of the state per thread: the same bits
+        for cpt in (1, 2):
+            ops.force_linrec_columns(cpt)
+            again = torch.zeros(6, H, dv, d, device="cuda")
+            try:
+                assert torch.equal(scan(xs, H, d, dv, None, hd, again, [4, 1], z=zs if kind == "channel" else None, **kw), whole)
+            finally:
+                ops.force_linrec_columns(0)
+            assert torch.equal(again, state)
         # the same in portions of 30, 2, 1, 1, ... tokens from a fresh state, the other slot order
         state2 = torch.zeros(6, H, dv, d, device="cuda")
         outs, at = [[], []], [0, 0]
