@@ -257,11 +257,16 @@ cudaError_t launch_scan_staged(int n_seqs, cudaStream_t stream, const float* pro
                                const int32_t* seq_slot, int n_heads, int dim, int vdim, float* state, float* out) {
   const dim3 grid((vdim + GROUPS * CPT - 1) / (GROUPS * CPT), n_heads, n_seqs);
   const long blocks = (long)grid.x * grid.y * grid.z;
-  if (blocks > fits(scan_smem<NPL>(PC, 3, CPT)) && blocks <= fits(scan_smem<NPL>(PC, 2, CPT)))
+  constexpr bool three_fit = scan_smem<NPL>(PC, 3, CPT) <= 226 * 1024;      // a block's limit
+  if constexpr (!three_fit)
     return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
                                              seq_slot, n_heads, dim, vdim, state, out);
-  return launch_scan<NPL, PC, VEC, 3, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
-                                           seq_slot, n_heads, dim, vdim, state, out);
+  else if (blocks > fits(scan_smem<NPL>(PC, 3, CPT)) && blocks <= fits(scan_smem<NPL>(PC, 2, CPT)))
+    return launch_scan<NPL, PC, VEC, 2, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                             seq_slot, n_heads, dim, vdim, state, out);
+  else
+    return launch_scan<NPL, PC, VEC, 3, CPT>(grid, stream, proj, ld, q_off, k_off, v_off, decay, head_decay, seq_row0,
+                                             seq_slot, n_heads, dim, vdim, state, out);
 }
 
 int g_force_cpt = 0;
@@ -293,7 +298,7 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
     SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: seqs=%d heads=%d dim=%d vdim=%d", n_seqs, n_heads, dim, vdim);
   if ((decay == nullptr) == (head_decay == nullptr))
     SB_FAIL(SB_ERR_ARG, "sb_linrec_scan: exactly one of the two kinds of decay is given");
-  if (dim > 16 * LANES) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: key size %d is above %d", dim, 16 * LANES);
+  if (dim > 32 * LANES) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: key size %d is above %d", dim, 32 * LANES);
   if (n_heads > 65535 || n_seqs > 65535) SB_FAIL(SB_ERR_UNSUPPORTED, "sb_linrec_scan: %d heads, %d sequences", n_heads, n_seqs);
   const int npl = (dim + LANES - 1) / LANES;
   // 16-byte copies when every staged stretch starts on a 16-byte boundary
@@ -308,7 +313,8 @@ extern "C" int sb_linrec_scan(const float* proj, int ld, int q_off, int k_off, i
   else if (npl <= 2) SB_LINREC_LAUNCH(2);
   else if (npl <= 4) SB_LINREC_LAUNCH(4);
   else if (npl <= 8) SB_LINREC_LAUNCH(8);
-  else SB_LINREC_LAUNCH(16);
+  else if (npl <= 16) SB_LINREC_LAUNCH(16);
+  else SB_LINREC_LAUNCH(32);
 #undef SB_LINREC_LAUNCH
 #undef SB_LINREC_ARGS
   if (e != cudaSuccess) SB_FAIL(SB_ERR_CUDA, "sb_linrec_scan: launch failed: %s", cudaGetErrorString(e));

@@ -243,7 +243,7 @@ def scan(seqs_proj, H, d, dv, decay, head_decay, state, slots, q_scale=1.0, k_sc
     return out.float().cpu()
 
 
-@pytest.mark.parametrize("H,d,dv", [(2, 16, 12), (1, 24, 40), (3, 40, 33), (2, 64, 64), (1, 128, 9), (1, 200, 17), (5, 5, 3)])
+@pytest.mark.parametrize("H,d,dv", [(2, 16, 12), (1, 24, 40), (3, 40, 33), (2, 64, 64), (1, 128, 9), (1, 200, 17), (5, 5, 3), (1, 300, 10)])
 def test_linear_recurrence_kernels(H, d, dv):
     """Both kinds of decay; prompts against token by token; two sequences side by side in slots
     that are not in order; key sizes on every register variant and between them."""
