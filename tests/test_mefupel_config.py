@@ -157,3 +157,20 @@ def test_polynorm_is_scale_free_in_its_input():
     a = pf.polynorm_ff(h, W, "", 0.0)
     b = pf.polynorm_ff(3.0 * h, W, "", 0.0)
     assert torch.allclose(a, b)
+
+
+def test_random_model_folder_reads_back(tmp_path):
+    """`write_random_model` on a Mefupel configuration: every requested tensor with its shape, the
+    same bits for the same seed, and the plain implementation runs on the folder."""
+    import plain_model as pm
+    from sonicboom_b200 import write_random_model
+    cfg = CONFIGS["A"]
+    write_random_model(tmp_path / "a", cfg, seed=4, std=0.05, bias_std=0.1, norm_std=0.1)
+    write_random_model(tmp_path / "b", cfg, seed=4, std=0.05, bias_std=0.1, norm_std=0.1)
+    _, ta = pm.read_model_dir(tmp_path / "a")
+    _, tb = pm.read_model_dir(tmp_path / "b")
+    want = {r.name: tuple(r.shape) for r in tensor_requests(spec_from_config_dict(cfg)[1])}
+    assert {n: tuple(t.shape) for n, t in ta.items()} == want
+    assert all(torch.equal(ta[n], tb[n]) for n in ta)
+    logits = pf.forward(cfg, ta, [1, 2, 3, 4, 5])
+    assert tuple(logits.shape) == (5, cfg["vocab"]) and bool(torch.isfinite(logits).all())
