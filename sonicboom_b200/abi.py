@@ -55,7 +55,7 @@ CORE = {
     "sb_polynorm": ("i", "piipifpis"),
     "sb_attn_prep": ("i", "piiiiiiiiiiiippppifppppipipiis"),
     "sb_attn_unrotate": ("i", "ppiiiiiipps"),
-    "sb_linrec_prep": ("i", "piiiiiiffiipppfs"),
+    "sb_linrec_prep": ("i", "piiiiiiffiipppfppiiis"),
     "sb_linrec_scan": ("i", "piiiippippiiipps"),
     "sb_linrec_force_columns": ("v", "i"),
     "sb_linrec_out": ("i", "ppiiiiipifpis"),

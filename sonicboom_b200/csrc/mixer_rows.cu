@@ -261,10 +261,14 @@ attn_unrotate_kernel(const T* in, T* out, int n_heads, int hd, int vdim, int int
 }
 
 // ---------------------------------------------------------------------- linear recurrence
+// With `a2` the decay logits are worked out here: z[t, c] = bias[c] + sum_r a2[c, r] * proj[t, a1_off + r]
+// (r ascending, float32), the second half of a low-rank map whose first half came with the projection.
+template <typename TA>
 __global__ void linrec_prep_kernel(float* proj, int ld, int q_off, int k_off, int n_heads, int dim,
                                    float q_scale, float k_scale, int rot, int interleaved,
                                    const float* __restrict__ inv_freq, const int32_t* row_pos, size_t n_rows,
-                                   float* z, float inv_tau) {
+                                   float* z, float inv_tau, const TA* __restrict__ a2, const TA* __restrict__ a2_bias,
+                                   int rank, int a1_off) {
   sb_pdl_launch();
   sb_pdl_wait();
   const size_t per_row = (size_t)n_heads * dim;
@@ -273,7 +277,15 @@ __global__ void linrec_prep_kernel(float* proj, int ld, int q_off, int k_off, in
     const size_t t = e / per_row;
     const int at = (int)(e % per_row), c = at % dim;
     if (z) {
-      const float u = z[e];
+      float u;
+      if (a2) {
+        const float* low = proj + t * ld + a1_off;
+        const TA* w = a2 + (size_t)at * rank;
+        u = sb_to_f32<TA>(a2_bias[at]);
+        for (int r = 0; r < rank; ++r) u = fmaf(sb_to_f32<TA>(w[r]), low[r], u);
+      } else {
+        u = z[e];
+      }
       const float ls = fminf(u, 0.0f) - log1pf(expf(-fabsf(u)));      // log sigmoid(u)
       z[e] = expf(ls * inv_tau);
     }
@@ -426,14 +438,19 @@ extern "C" int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows
 
 extern "C" int sb_linrec_prep(float* proj, int n_rows, int ld, int q_off, int k_off, int n_heads, int dim,
                               float q_scale, float k_scale, int rot, int interleaved, const float* inv_freq,
-                              const int32_t* row_pos, float* z, float inv_tau, cudaStream_t stream) {
+                              const int32_t* row_pos, float* z, float inv_tau, const void* a2,
+                              const void* a2_bias, int a2_dtype, int rank, int a1_off, cudaStream_t stream) {
   if (n_rows <= 0 || n_heads <= 0 || dim <= 0 || !proj) SB_FAIL(SB_ERR_ARG, "sb_linrec_prep: rows=%d heads=%d dim=%d", n_rows, n_heads, dim);
   if (rot < 0 || rot % 2 || rot > dim || (rot > 0 && (!inv_freq || !row_pos)))
     SB_FAIL(SB_ERR_ARG, "sb_linrec_prep: %d rotated of %d dimensions (even, at most dim, with a table)", rot, dim);
+  if (a2 && (!z || !a2_bias || rank <= 0 || a1_off < 0 || !sb_valid_dtype(a2_dtype)))
+    SB_FAIL(SB_ERR_ARG, "sb_linrec_prep: the decay map needs z, its bias, a rank and a valid dtype (rank=%d dtype=%d)", rank, a2_dtype);
   const size_t n = (size_t)n_rows * n_heads * dim;
-  sb_launch<SB_K_ELEMENTWISE>(linrec_prep_kernel, dim3(grid_for(n, 256)), dim3(256), 0, stream, proj, ld, q_off, k_off,
-                              n_heads, dim, q_scale, k_scale, rot, interleaved, inv_freq, row_pos, (size_t)n_rows, z,
-                              inv_tau);
+  SB_DISPATCH_DTYPE(a2 ? a2_dtype : SB_F32, TA, {
+    sb_launch<SB_K_ELEMENTWISE>(linrec_prep_kernel<TA>, dim3(grid_for(n, 256)), dim3(256), 0, stream, proj, ld, q_off,
+                                k_off, n_heads, dim, q_scale, k_scale, rot, interleaved, inv_freq, row_pos,
+                                (size_t)n_rows, z, inv_tau, (const TA*)a2, (const TA*)a2_bias, rank, a1_off);
+  });
   SB_CHECK_LAUNCH("sb_linrec_prep");
   return SB_OK;
 }

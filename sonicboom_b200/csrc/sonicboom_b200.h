@@ -238,10 +238,13 @@ int sb_attn_unrotate(const void* in, void* out, int dtype, int n_rows, int n_hea
                      sb_stream_t stream);
 /* In place on projection rows: q (at q_off) and k (at k_off), [n_heads x dim] each, are rotated
  * (the first `rot` of every head, pairs as in sb_attn_prep) and multiplied by q_scale / k_scale; z
- * [rows, n_heads * dim], if given, becomes exp(logsigmoid(z) * inv_tau). */
+ * [rows, n_heads * dim], if given, becomes exp(logsigmoid(z) * inv_tau).  With a2 [n_heads * dim,
+ * rank] and a2_bias the logits are made here first: z = a2 . proj[row, a1_off : a1_off + rank] + a2_bias
+ * (z is then written only). */
 int sb_linrec_prep(float* proj, int n_rows, int ld, int q_off, int k_off, int n_heads, int dim,
                    float q_scale, float k_scale, int rot, int interleaved, const float* inv_freq,
-                   const int32_t* row_pos, float* z, float inv_tau, sb_stream_t stream);
+                   const int32_t* row_pos, float* z, float inv_tau, const void* a2, const void* a2_bias,
+                   int a2_dtype, int rank, int a1_off, sb_stream_t stream);
 /* S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t per head and sequence, token by token, from
  * and to state [slot, n_heads, vdim, dim] float32; a_t from decay [rows, n_heads * dim] or, one
  * value per head, from head_decay [n_heads] (exactly one of them).  out [rows, n_heads, vdim]. */

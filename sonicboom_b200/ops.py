@@ -818,15 +818,25 @@ def attn_unrotate(x: torch.Tensor, out: torch.Tensor, n_heads: int, head_size: i
 # ---------------------------------------------------------------------- linear recurrence
 def linrec_prep(proj: torch.Tensor, q_off: int, k_off: int, n_heads: int, dim: int, q_scale: float,
                 k_scale: float, rotary_dim: int, interleaved: bool, inv_freq: torch.Tensor | None, row_pos,
-                z: torch.Tensor | None = None, inv_tau: float = 1.0) -> torch.Tensor:
+                z: torch.Tensor | None = None, inv_tau: float = 1.0, low_rank: tuple | None = None) -> torch.Tensor:
     """In place: rotates and scales the q and k of the projection rows; turns decay logits `z`
-    [rows, heads * dim] into decays exp(logsigmoid(z) * inv_tau)."""
+    [rows, heads * dim] into decays exp(logsigmoid(z) * inv_tau).  `low_rank` = (a2 [heads * dim, rank],
+    bias, a1_off): the logits are made here first, a2 times the rank values at `a1_off` of every
+    projection row plus the bias, and `z` only receives the decays."""
     n, ld = proj.shape
+    a2 = bias = None
+    rank = a1_off = 0
+    if low_rank is not None:
+        a2, bias, a1_off = low_rank
+        rank = a2.shape[1]
+        assert z is not None and a2.dtype == bias.dtype and a2.shape[0] == bias.numel() == n_heads * dim
+        assert 0 <= a1_off and a1_off + rank <= ld
     assert proj.dtype == torch.float32 and max(q_off, k_off) + n_heads * dim <= ld
     assert z is None or (z.dtype == torch.float32 and tuple(z.shape) == (n, n_heads * dim))
     _check(lib().sb_linrec_prep(_ptr(proj), n, ld, q_off, k_off, n_heads, dim, ctypes.c_float(q_scale),
                                 ctypes.c_float(k_scale), rotary_dim, 1 if interleaved else 0, _ptr(inv_freq),
-                                _i32(row_pos, "row_pos"), _ptr(z), ctypes.c_float(inv_tau), _stream()),
+                                _i32(row_pos, "row_pos"), _ptr(z), ctypes.c_float(inv_tau), _ptr(a2), _ptr(bias),
+                                _code(a2.dtype) if a2 is not None else 0, rank, a1_off, _stream()),
            "linrec_prep")
     return proj
 

@@ -14,8 +14,8 @@ divided by its root mean square (`eps`) and, with `norm_weight` = a tensor name,
 that weight [vdim], which all heads share; the heads are concatenated, multiplied by silu(G h)
 and projected by O.
 
-q, k, v and g are one product; decays, the rotation, the state and the recurrence are float32
-whatever the activation dtype.  The state (float32 [heads, vdim, head_dim]) is fixed-size
+q, k, v, g and the first half of the decay map are one product; the map's second half, the
+decays, the rotation, the state and the recurrence are float32 whatever the activation dtype.  The state (float32 [heads, vdim, head_dim]) is fixed-size
 per-sequence state of the cache, zeroed when a slot is taken and carried from step to step; the
 recurrence runs token by token for prompts, portions and single tokens alike.
 
@@ -63,7 +63,8 @@ class LinearRecurrence(Mixer):
             self.rot, self.inv_freq = spec.position.rotary_dim, pe.inv_freq
         self.k_off, self.v_off = self.h * self.dim, 2 * self.h * self.dim
         self.g_off = self.v_off + self.h * self.vd
-        self.w_in = self.w_a1 = self.w_a2 = self.b_a2 = self.norm_w = self.w_o = None
+        self.w_in = self.w_a2 = self.b_a2 = self.norm_w = self.w_o = None
+        self.a1_off = 0
 
     def state_need(self):
         return StateNeed((self.h, self.vd, self.dim), torch.float32)
@@ -84,14 +85,17 @@ class LinearRecurrence(Mixer):
     def bind(self, get):
         from ..config.specs import ConfigError
         p = self.spec.prefix
-        self.w_in = _cat([get(p + n) for n in ("q", "k", "v", "g")])
+        parts = [get(p + n) for n in ("q", "k", "v", "g")]
         self.w_o = get(p + "o")
         if self.decay == "low_rank":
-            self.w_a1, self.w_a2, self.b_a2 = get(p + "a1"), get(p + "a2"), get(p + "a2.b")
-            if self.w_a1.shape[0] != self.w_a2.shape[1]:
-                raise ConfigError(f"{p}a1 has {self.w_a1.shape[0]} rows, {p}a2 {self.w_a2.shape[1]} columns")
-            if self.w_a1.dtype != self.w_a2.dtype:
-                self.w_a1, self.w_a2 = self.w_a1.float(), self.w_a2.float()
+            w_a1, self.w_a2, self.b_a2 = get(p + "a1"), get(p + "a2"), get(p + "a2.b")
+            if w_a1.shape[0] != self.w_a2.shape[1]:
+                raise ConfigError(f"{p}a1 has {w_a1.shape[0]} rows, {p}a2 {self.w_a2.shape[1]} columns")
+            if self.w_a2.dtype != self.b_a2.dtype:
+                self.w_a2, self.b_a2 = self.w_a2.float(), self.b_a2.float()
+            parts.append(w_a1)                       # the map's first half rides on the projection
+            self.a1_off = self.g_off + self.h * self.vd
+        self.w_in = _cat(parts)
         if self.norm_name:
             self.norm_w = get(p + self.norm_name)
 
@@ -101,14 +105,13 @@ class LinearRecurrence(Mixer):
         ops.linear(h, self.w_in, proj)
         z = None
         if self.decay == "low_rank":
-            low = torch.empty((rows, self.w_a1.shape[0]), dtype=self.w_a2.dtype, device=h.device)
-            ops.linear(h, self.w_a1, low)
             z = torch.empty((rows, self.h * self.dim), dtype=torch.float32, device=h.device)
-            ops.linear(low, self.w_a2, z, ops.EPI_BIAS, bias=self.b_a2)
-        if z is not None or self.rot > 0 or self.q_scale != 1.0 or self.k_scale != 1.0:
             ops.linrec_prep(proj, 0, self.k_off, self.h, self.dim, self.q_scale, self.k_scale, self.rot,
-                            self.interleaved, self.inv_freq, plan.row_pos, z,
-                            1.0 / self.tau if z is not None else 1.0)
+                            self.interleaved, self.inv_freq, plan.row_pos, z, 1.0 / self.tau,
+                            low_rank=(self.w_a2, self.b_a2, self.a1_off))
+        elif self.rot > 0 or self.q_scale != 1.0 or self.k_scale != 1.0:
+            ops.linrec_prep(proj, 0, self.k_off, self.h, self.dim, self.q_scale, self.k_scale, self.rot,
+                            self.interleaved, self.inv_freq, plan.row_pos)
         o = torch.empty((rows, self.h, self.vd), dtype=torch.float32, device=h.device)
         ops.linrec_scan(proj, 0, self.k_off, self.v_off, plan, self.h, self.dim, self.vd, z, self.head_decay,
                         ctx.state(), o)

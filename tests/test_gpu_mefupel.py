@@ -306,6 +306,26 @@ def test_linear_recurrence_kernels(H, d, dv):
         assert torch.equal(state2[2], state[4]) and torch.equal(state2[5], state[1])
 
 
+def test_decay_map_in_the_prep_kernel():
+    """The second half of the low-rank decay map, worked out where the decays are made."""
+    g = torch.Generator().manual_seed(12)
+    for rows, H, d, rank, dt in ((5, 2, 16, 4, torch.float32), (70, 3, 40, 24, torch.bfloat16), (9, 1, 8, 1, torch.bfloat16)):
+        extra = 11
+        proj = torch.randn(rows, 2 * H * d + extra + rank, generator=g)
+        a2, b = (torch.randn(H * d, rank, generator=g) * 0.5).to(dt), torch.randn(H * d, generator=g).to(dt)
+        zl = b.double() + proj[:, 2 * H * d + extra:].double() @ a2.double().T
+        ref = torch.exp(torch.nn.functional.logsigmoid(zl) / 3.0)
+        dev = proj.cuda()
+        z = torch.empty(rows, H * d, device="cuda")
+        pos = torch.zeros(rows, dtype=torch.int32, device="cuda")
+        ops.linrec_prep(dev, 0, H * d, H, d, 2.0, 0.5, 0, False, None, pos, z, 1.0 / 3.0,
+                        low_rank=(a2.cuda(), b.cuda(), 2 * H * d + extra))
+        assert rel_err(z, ref) < 1e-6
+        assert rel_err(dev[:, :H * d], proj[:, :H * d].double() * 2.0) < 1e-7
+        assert rel_err(dev[:, H * d:2 * H * d], proj[:, H * d:2 * H * d].double() * 0.5) < 1e-7
+        assert torch.equal(dev[:, 2 * H * d:].cpu(), proj[:, 2 * H * d:])
+
+
 # ------------------------------------------------------------------ mechanisms alone: one-layer models
 ONE_LAYER = {
     "attention": model(64, 32, [layer("attention", attention(2, 1, 16, 16, window=11, dims=6))]),
