@@ -625,12 +625,12 @@ def mefupel_config(width, n_layers, ff, vocab, heads, kv_heads, dim, window, r_h
     the side-by-side layer in turn, every layer with its feed-forward; no loop (the weights are then
     what a step reads, as in the model beside it)."""
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-           "mask": {"size": window}, "rot": {"base": 250000.0, "dims": dim}}
-    left = dict(att, rot={"base": 10000.0, "dims": dim // 2})
-    right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"base": 1e6, "dims": r_dim},
-             "decay": [1.0 - 2.0 ** -(5 + i % 8) for i in range(r_heads)]}
+           "mask": {"size": window}, "rot": {"base": 500000.0, "dims": dim}}
+    left = dict(att, rot={"base": 20000.0, "dims": dim // 2})
+    right = {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "rot": {"base": 100000.0, "dims": r_dim},
+             "decay": [0.9 + 0.099 * (i + 1) / r_heads for i in range(r_heads)]}
     kinds = [("attention", att), ("attention", att),
-             ("gla", {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 16.0, "decay_rank": rank}),
+             ("gla", {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "tau": 12.0, "decay_rank": rank}),
              ("parallel", {"left": left, "right": right})]
     layers = [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": ff}}
               for i in range(n_layers)]

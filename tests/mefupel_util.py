@@ -50,8 +50,8 @@ CONFIGS = {
     # the side-by-side layer first and looped once; one recurrence head; key sizes 24 and 40; a
     # window of one key; an inner size that is no multiple of 8; head size 64 and 128 kernels
     "B": model(150, 96, [
-        layer("parallel", {"left": attention(2, 2, 64, 64, window=70, base=250000.0),
-                           "right": retention(1, 24, 40, [0.97], base=1e6)}, ff=50),
+        layer("parallel", {"left": attention(2, 2, 64, 64, window=70, base=300000.0),
+                           "right": retention(1, 24, 40, [0.97], base=2e6)}, ff=50),
         layer("gla", gla(3, 40, 33, tau=1.0, rank=8)),
         layer("attention", attention(6, 3, 128, 64, window=1, dims=2, base=100.0), ff=64),
         layer("gla", gla(1, 16, 16, tau=30.0, rank=2), ff=16),

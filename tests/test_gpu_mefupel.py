@@ -173,7 +173,7 @@ ATTENTION_CASES = {
     # keys as values, whole-projection norms, a sink, halves; head sizes of the mma.sync and of the tensor-memory kernels
     "sink_32": dict(hq=4, hkv=1, dim=32, vdim=32, window=20, scale=0.3, rot=16, layout="halves", base=10000.0,
                     rotate_values=False, qk_norm=True, keys_as_values=True, sink=True),
-    "sink_64": dict(hq=4, hkv=2, dim=64, vdim=64, window=130, scale=0.2, rot=64, layout="halves", base=1e6,
+    "sink_64": dict(hq=4, hkv=2, dim=64, vdim=64, window=130, scale=0.2, rot=64, layout="halves", base=2e6,
                     rotate_values=False, qk_norm=True, keys_as_values=True, sink=True),
     "sink_128": dict(hq=6, hkv=2, dim=128, vdim=128, window=100, scale=0.15, rot=64, layout="halves", base=1e4,
                      rotate_values=False, qk_norm=True, keys_as_values=True, sink=True),
